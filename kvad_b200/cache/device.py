@@ -28,10 +28,11 @@ from .pages import PAGE_SIZE, SlotBook
 class KVView:
     """One cache entry's pages as a mixer sees them during a step."""
     k_pages: torch.Tensor          # [pages, kv heads, page size, head size]
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]    # [pages, kv heads, page size, value size]; None: the group keeps no values
     page_table: torch.Tensor       # int32 [sequences of the step, table width], this group's
     window: Optional[int]
     page_size: int
+    keep_first: int = 0
 
 
 class DeviceCache:
@@ -50,23 +51,24 @@ class DeviceCache:
         per_seq = max_positions if max_positions else self.max_tokens
         self.table_width = max(1, -(-per_seq // page_size))
 
-        self.kv: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+        self.kv: dict[int, tuple[torch.Tensor, Optional[torch.Tensor]]] = {}
         self.state: dict[int, torch.Tensor] = {}
-        pages_per_group, windows = [], []
+        pages_per_group, windows, keep_first = [], [], []
         self._kv_group_index: dict[int, int] = {}     # layout group -> index among kv groups (SlotBook's numbering)
         for g, group in enumerate(layout.groups):
             need = group.need
             if isinstance(need, KVNeed):
-                shape = (len(group.entries), n_pages, need.n_kv_heads, page_size, need.head_dim)
-                self.kv[g] = (torch.empty(shape, dtype=dtype, device=self.device),
-                              torch.empty(shape, dtype=dtype, device=self.device))
+                shape = (len(group.entries), n_pages, need.n_kv_heads, page_size)
+                self.kv[g] = (torch.empty((*shape, need.head_dim), dtype=dtype, device=self.device),
+                              torch.empty((*shape, need.v_dim), dtype=dtype, device=self.device) if need.v_dim else None)
                 self._kv_group_index[g] = len(pages_per_group)
                 pages_per_group.append(n_pages)
                 windows.append(need.window)
+                keep_first.append(need.keep_first if need.window is not None else 0)
             elif isinstance(need, StateNeed):
                 self.state[g] = torch.zeros((len(group.entries), self.n_slots, *need.shape),
                                             dtype=need.dtype, device=self.device)
-        self.book = SlotBook(self.n_slots, pages_per_group, windows, page_size, max_positions)
+        self.book = SlotBook(self.n_slots, pages_per_group, windows, page_size, max_positions, keep_first)
 
     # -- slots -------------------------------------------------------------------
     def acquire(self) -> int:
@@ -92,7 +94,7 @@ class DeviceCache:
         g, i = self.layout.place(entry)
         k, v = self.kv[g]
         need = self.layout.groups[g].need
-        return KVView(k[i], v[i], page_tables[g], need.window, self.page_size)
+        return KVView(k[i], None if v is None else v[i], page_tables[g], need.window, self.page_size, need.keep_first)
 
     def state_view(self, entry: int) -> torch.Tensor:
         """`[slots, *shape]` of one entry; rows are indexed by slot id."""
@@ -103,7 +105,7 @@ class DeviceCache:
     def bytes(self) -> int:
         n = 0
         for k, v in self.kv.values():
-            n += k.numel() * k.element_size() * 2
+            n += k.numel() * k.element_size() + (0 if v is None else v.numel() * v.element_size())
         for s in self.state.values():
             n += s.numel() * s.element_size()
         return n

@@ -20,12 +20,20 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every position is kept
+    value_dim: Optional[int] = None  # None: values are as long as keys; 0: no values are kept (they are read from the keys)
+    keep_first: int = 0              # with a window: the first positions stay in reach of every later query
 
     def __post_init__(self):
         if self.n_kv_heads <= 0 or self.head_dim <= 0:
             raise ValueError("a key/value cache needs positive head count and head size")
         if self.window is not None and self.window <= 0:
             raise ValueError("a window must be positive")
+        if (self.value_dim is not None and self.value_dim < 0) or self.keep_first < 0:
+            raise ValueError("value size and kept first positions cannot be negative")
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -80,5 +88,5 @@ class CacheLayout:
         total = 0
         for g in self.groups:
             if isinstance(g.need, KVNeed):
-                total += 2 * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * element_size
+                total += len(g.entries) * g.need.n_kv_heads * (g.need.head_dim + g.need.v_dim) * element_size
         return total

@@ -63,9 +63,14 @@ class SlotBook:
     """Slots, their lengths, and their pages in every key/value group."""
 
     def __init__(self, n_slots: int, pages_per_group: Sequence[int], windows: Sequence[Optional[int]],
-                 page_size: int = PAGE_SIZE, max_positions: Optional[int] = None):
+                 page_size: int = PAGE_SIZE, max_positions: Optional[int] = None,
+                 keep_first: Optional[Sequence[int]] = None):
         if len(pages_per_group) != len(windows):
             raise ValueError("one window entry (or None) per group")
+        keep_first = list(keep_first) if keep_first is not None else [0] * len(windows)
+        if len(keep_first) != len(windows):
+            raise ValueError("one count of kept first positions per group")
+        self.keep_first = keep_first
         self.page_size = int(page_size)
         self.max_positions = max_positions
         self.slots = IdPool(n_slots, "slot")
@@ -128,14 +133,16 @@ class SlotBook:
         return first
 
     def trim_windows(self, slot: int) -> None:
-        """Drops pages that no later query of a windowed group can reach."""
+        """Drops pages that no later query of a windowed group can reach (pages that hold one of the
+        group's kept first positions stay)."""
         n = self.length[slot]
         for g, w in enumerate(self.windows):
             if w is None:
                 continue
             first_needed = max(0, n - w + 1)     # the next query sits at position n
             table = self.pages[slot][g]
-            for i in range(min(len(table), first_needed // self.page_size)):
+            kept = -(-self.keep_first[g] // self.page_size)
+            for i in range(kept, min(len(table), first_needed // self.page_size)):
                 if table[i] >= 0:
                     self.pools[g].give_back(table[i])
                     table[i] = -1

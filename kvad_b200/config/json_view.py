@@ -84,13 +84,15 @@ class JsonView:
 
 
 def read_model_type(view: JsonView) -> str:
-    """`model_type`, else the first of `architectures`, lower-cased
-    (crates/llm/src/model/mod.rs:326-332)."""
+    """`model_type`, else the first of `architectures` (crates/llm/src/model/mod.rs:326-332), else
+    `architecture`; lower-cased."""
     mt = view.text("model_type")
     if mt is None:
         archs = view.get("architectures")
         if isinstance(archs, list) and archs and isinstance(archs[0], str):
             mt = archs[0]
+    if mt is None:
+        mt = view.text("architecture")
     if mt is None:
         raise ConfigError("config.json has neither model_type nor architectures")
     return mt.lower()

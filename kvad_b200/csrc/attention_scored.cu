@@ -1,0 +1,387 @@
+// Softmax attention over the paged cache with everything a score can be given on its way to the softmax,
+// on the CUDA cores in 32-bit arithmetic, for prompts and for single-token rows alike:
+//
+//   s = (q . k) * scale;  s = cap * tanh(s / cap)  (cap > 0);  s -= slope_h * (i - j)  (slope_span > 0,
+//   slope_h = 2^(-slope_span * (h + 1) / n_heads));  query i sees key j if j <= i and
+//   (window <= 0 or i - j < window or j < keep_first).
+//
+// Keys and values may differ in size (dk, dv), several query heads may share a key/value head, and the
+// values may BE the keys' first dv entries (`v_pages` = `k_pages` with the keys' row stride): a latent
+// cache read by queries that were carried into the latent's space.  The output may be multiplied by
+// sigmoid(gate) where it is written.
+//
+// A block works a tile of 32 (token, head) pairs that share one key/value head - 32 / hp consecutive
+// tokens of one sequence times hp heads of the group (prompts: few heads, many tokens; single-token rows:
+// one token, all heads of the group) - against the keys tile by tile: a tile of keys and values comes into
+// shared memory once for all 32 pairs.  Warp w owns pairs 8w .. 8w+7: for the scores a lane takes keys
+// lane (and lane + 32) of the tile for all eight, maxima and sums meet by shuffles, the weights go through
+// shared memory, and for the output a lane owns dimensions lane, lane + 32, ...  Tiles of keys that no
+// pair of the block sees (before every window and past the kept first tokens) are skipped, so pages that
+// the cache has dropped are never touched.
+//
+// Also here: the cache writes that go with it - keys and values of different sizes with the values blended
+// with another layer's (`kv_store_blend`), and a latent row normalised, its rotary part turned, and stored
+// (`latent_store`).
+#include "common.cuh"
+
+using namespace kvad;
+
+namespace {
+
+constexpr int TR = 32, THREADS = 128, RPW = TR / (THREADS / 32), PAGE = 64;
+
+struct ScoredArgs {
+  const void* q; int64_t ld_q;
+  void* out; int64_t ld_out;
+  const void* gate; int64_t ld_gate;
+  const int* seq_starts; const int* kv_lens; const int* page_table; int table_width;
+  const void* k_pages; const void* v_pages;
+  int64_t k_page_stride, k_head_stride, v_page_stride, v_head_stride;   // in elements
+  int ld_k, ld_v;                                                       // row strides inside a page
+  int n_heads, n_kv_heads, dk, dv, hp, v_alias;
+  float scale, softcap, slope_span;
+  int window, keep_first;
+};
+
+template <typename T, int KPL, int DPL>
+__global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredArgs a) {
+  constexpr int TK = 32 * KPL;
+  extern __shared__ float smem[];
+  const int dk = a.dk, dv = a.dv, ldks = dk + 1, ldvs = a.v_alias ? ldks : dv;
+  float* Qs = smem;                                   // [TR][dk]
+  float* Ks = Qs + TR * dk;                           // [TK][dk + 1]
+  float* Vs = a.v_alias ? Ks : Ks + TK * ldks;        // [TK][ldvs]
+  float* Ps = a.v_alias ? Ks + TK * ldks : Vs + TK * dv;   // [TR][TK]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int hp = a.hp, tok = TR / hp;
+  const int group = a.n_heads / a.n_kv_heads, chunks = (group + hp - 1) / hp;
+  const int s = blockIdx.y, kvh = blockIdx.z / chunks, chunk = blockIdx.z % chunks;
+  const int start = a.seq_starts[s], n_new = a.seq_starts[s + 1] - start, tok0 = blockIdx.x * tok;
+  if (tok0 >= n_new) return;
+  const int n_tok = n_new - tok0 < tok ? n_new - tok0 : tok;
+  const int h0 = kvh * group + chunk * hp, n_h = group - chunk * hp < hp ? group - chunk * hp : hp;
+  const int pos0 = a.kv_lens[s] - n_new + tok0, last_pos = pos0 + n_tok - 1;
+  const int* pages = a.page_table + (int64_t)s * a.table_width;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* q = (const T*)a.q;
+
+  for (int i = tid; i < TR * dk; i += THREADS) {
+    const int r = i / dk, d = i - r * dk, ti = r / hp, hi = r - ti * hp;
+    Qs[i] = (ti < n_tok && hi < n_h) ? to_f32(q[(int64_t)(start + tok0 + ti) * a.ld_q + (int64_t)(h0 + hi) * dk + d]) : 0.f;
+  }
+  // what each of the warp's pairs is: its position, whether it exists, its head's slope
+  int row_pos[RPW];
+  bool row_live[RPW];
+  float row_slope[RPW];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    const int row = warp * RPW + r, ti = row / hp, hi = row - ti * hp;
+    row_live[r] = ti < n_tok && hi < n_h;
+    row_pos[r] = pos0 + ti;
+    row_slope[r] = a.slope_span > 0.f ? exp2f(-a.slope_span * (float)(h0 + hi + 1) / (float)a.n_heads) : 0.f;
+  }
+  float acc[RPW][DPL], run_max[RPW], run_sum[RPW];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    run_max[r] = -INFINITY;
+    run_sum[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[r][i] = 0.f;
+  }
+  const int first_key = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;   // of the block's first token
+  const T* kp = (const T*)a.k_pages;
+  const T* vp = (const T*)a.v_pages;
+  for (int t = 0; t <= last_pos / TK; ++t) {
+    const int key0 = t * TK;
+    if (key0 + TK <= first_key && key0 >= a.keep_first) continue;       // (the same for every thread of the block)
+    __syncthreads();                                                    // the tile before has been used up (and Qs is written)
+    const int page = pages[key0 / PAGE], in_page = key0 % PAGE;
+    const T* kt = kp + (int64_t)page * a.k_page_stride + (int64_t)kvh * a.k_head_stride + (int64_t)in_page * a.ld_k;
+    for (int i = tid; i < TK * dk; i += THREADS) {
+      const int k = i / dk, d = i - k * dk;
+      Ks[k * ldks + d] = key0 + k <= last_pos ? to_f32(kt[(int64_t)k * a.ld_k + d]) : 0.f;   // (a place no row sees yet may hold anything)
+    }
+    if (!a.v_alias) {
+      const T* vt = vp + (int64_t)page * a.v_page_stride + (int64_t)kvh * a.v_head_stride + (int64_t)in_page * a.ld_v;
+      for (int i = tid; i < TK * dv; i += THREADS) {
+        const int k = i / dv, d = i - k * dv;
+        Vs[i] = key0 + k <= last_pos ? to_f32(vt[(int64_t)k * a.ld_v + d]) : 0.f;
+      }
+    }
+    __syncthreads();
+    float sc[RPW][KPL];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r)
+#pragma unroll
+      for (int j = 0; j < KPL; ++j) sc[r][j] = 0.f;
+    const float* qw = Qs + warp * RPW * dk;
+    for (int d = 0; d < dk; d += 4) {
+      float kv[KPL][4];
+#pragma unroll
+      for (int j = 0; j < KPL; ++j) {
+        const float* kr = Ks + (lane + 32 * j) * ldks + d;
+        kv[j][0] = kr[0]; kv[j][1] = kr[1]; kv[j][2] = kr[2]; kv[j][3] = kr[3];
+      }
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const float4 qv = *reinterpret_cast<const float4*>(qw + r * dk + d);
+#pragma unroll
+        for (int j = 0; j < KPL; ++j)
+          sc[r][j] = fmaf(qv.w, kv[j][3], fmaf(qv.z, kv[j][2], fmaf(qv.y, kv[j][1], fmaf(qv.x, kv[j][0], sc[r][j]))));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int pos = row_pos[r];
+      float v[KPL];
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < KPL; ++j) {
+        const int key = key0 + lane + 32 * j;
+        v[j] = -INFINITY;
+        if (row_live[r] && key <= pos && (a.window <= 0 || pos - key < a.window || key < a.keep_first)) {
+          float x = sc[r][j] * a.scale;
+          if (a.softcap > 0.f) x = a.softcap * tanhf(x / a.softcap);
+          v[j] = x - row_slope[r] * (float)(pos - key);
+        }
+        tile_max = fmaxf(tile_max, v[j]);
+      }
+      tile_max = warp_max(tile_max);
+      const float new_max = fmaxf(run_max[r], tile_max);
+      const float base = new_max == -INFINITY ? 0.f : new_max;
+      const float keep = run_max[r] == -INFINITY ? 0.f : expf(run_max[r] - base);
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < KPL; ++j) {
+        const float p = v[j] == -INFINITY ? 0.f : expf(v[j] - base);
+        Ps[(warp * RPW + r) * TK + lane + 32 * j] = p;
+        psum += p;
+      }
+      run_sum[r] = run_sum[r] * keep + warp_sum(psum);
+      run_max[r] = new_max;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[r][i] *= keep;
+    }
+    __syncwarp();
+    const float* pw = Ps + warp * RPW * TK;
+    for (int k = 0; k < TK; k += 4) {
+      float4 pv[RPW];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) pv[r] = *reinterpret_cast<const float4*>(pw + r * TK + k);
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dv) {
+          const float x0 = Vs[k * ldvs + d], x1 = Vs[(k + 1) * ldvs + d], x2 = Vs[(k + 2) * ldvs + d], x3 = Vs[(k + 3) * ldvs + d];
+#pragma unroll
+          for (int r = 0; r < RPW; ++r)
+            acc[r][i] = fmaf(pv[r].w, x3, fmaf(pv[r].z, x2, fmaf(pv[r].y, x1, fmaf(pv[r].x, x0, acc[r][i]))));
+        }
+      }
+    }
+  }
+  T* out = (T*)a.out;
+  const T* gate = (const T*)a.gate;
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    if (!row_live[r]) continue;
+    const int row = warp * RPW + r, ti = row / hp, hi = row - ti * hp;
+    const float inv = 1.0f / run_sum[r];
+    const int64_t grow = start + tok0 + ti;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dv) {
+        float y = acc[r][i] * inv;
+        if (gate != nullptr) y *= 1.0f / (1.0f + expf(-to_f32(gate[grow * a.ld_gate + (int64_t)(h0 + hi) * dv + d])));
+        out[grow * a.ld_out + (int64_t)(h0 + hi) * dv + d] = from_f32<T>(y);
+      }
+    }
+  }
+}
+
+template <typename T, int KPL, int DPL>
+int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cudaStream_t stream) {
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(scored_attention_kernel<T, KPL, DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention (scored): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  const int tok = TR / a.hp, group = a.n_heads / a.n_kv_heads, chunks = (group + a.hp - 1) / a.hp;
+  dim3 grid((max_new + tok - 1) / tok, n_seqs, a.n_kv_heads * chunks);
+  kvad_launch(scored_attention_kernel<T, KPL, DPL>, grid, dim3(THREADS), smem, stream, a);
+  KVAD_CHECK_LAUNCH("attention_scored");
+  return KVAD_OK;
+}
+
+template <typename T>
+int dispatch_scored(const ScoredArgs& a, int n_seqs, int max_new, cudaStream_t stream) {
+  const size_t limit = 200 * 1024;
+  auto need = [&](int tk) {
+    return ((size_t)TR * a.dk + (size_t)tk * (a.dk + 1) + (a.v_alias ? 0 : (size_t)tk * a.dv) + (size_t)TR * tk) * sizeof(float);
+  };
+  const int kpl = need(64) <= limit ? 2 : 1;
+  const size_t smem = need(32 * kpl);
+  if (smem > limit) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): keys of %d and values of %d entries do not fit shared memory", a.dk, a.dv);
+  const int dpl = (a.dv + 31) / 32;
+#define KVAD_SC(K, D) return launch_scored<T, K, D>(a, n_seqs, max_new, smem, stream)
+#define KVAD_SC_D(K)                      \
+  do {                                    \
+    if (dpl <= 1) KVAD_SC(K, 1);          \
+    if (dpl <= 2) KVAD_SC(K, 2);          \
+    if (dpl <= 4) KVAD_SC(K, 4);          \
+    if (dpl <= 8) KVAD_SC(K, 8);          \
+    if (dpl <= 16) KVAD_SC(K, 16);        \
+  } while (0)
+  if (kpl == 2) KVAD_SC_D(2);
+  else KVAD_SC_D(1);
+#undef KVAD_SC_D
+#undef KVAD_SC
+  KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): values of %d entries are above this kernel's limit of 512", a.dv);
+}
+
+// Keys (dk a head) and values (dv a head) of a step's rows into their pages; with `v_other` the stored value is
+// (1 - lambda) v + lambda v_other, lambda a scalar in device memory (32-bit arithmetic, one rounding).
+template <typename T>
+__global__ void kv_store_blend_kernel(const T* __restrict__ k_src, int64_t ld_k, const T* __restrict__ v_src, int64_t ld_v,
+                                      const T* __restrict__ v_other, int64_t ld_o, const void* __restrict__ lambda, int lambda_f32,
+                                      const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                      const int* __restrict__ page_table, int table_width, T* __restrict__ k_pages,
+                                      T* __restrict__ v_pages, int n_rows, int n_kv, int dk, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int wk = n_kv * dk, wv = n_kv * dv, per_row = wk + wv;
+  const float lam = v_other != nullptr ? load_param(lambda, 0, lambda_f32) : 0.f;
+  const int64_t total = (int64_t)n_rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / per_row), c = (int)(i % per_row);
+    const int pos = row_pos[r];
+    const int64_t page = page_table[(int64_t)row_seq[r] * table_width + pos / PAGE];
+    if (c < wk) {
+      const int h = c / dk, d = c % dk;
+      k_pages[((page * n_kv + h) * PAGE + pos % PAGE) * dk + d] = k_src[(int64_t)r * ld_k + c];
+    } else {
+      const int cv = c - wk, h = cv / dv, d = cv % dv;
+      T v = v_src[(int64_t)r * ld_v + cv];
+      if (v_other != nullptr) v = from_f32<T>((1.0f - lam) * to_f32(v) + lam * to_f32(v_other[(int64_t)r * ld_o + cv]));
+      v_pages[((page * n_kv + h) * PAGE + pos % PAGE) * dv + d] = v;
+    }
+  }
+}
+
+// A warp per row: the first `rank` entries are RMS-normalised with a weight, the last `rot` entries turned by
+// the row's position (pairs interleaved or half apart), and the row goes to its place in pages of one head of
+// rank + rot entries.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_store_kernel(const T* __restrict__ src, int64_t ld, const void* __restrict__ w, int w_f32, float eps,
+                    const float* __restrict__ inv_freq, int interleaved, const int* __restrict__ row_seq,
+                    const int* __restrict__ row_pos, const int* __restrict__ page_table, int table_width,
+                    T* __restrict__ pages, int n_rows, int rank, int rot) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const T* x = src + (int64_t)r * ld;
+  const int pos = row_pos[r];
+  const int64_t page = page_table[(int64_t)row_seq[r] * table_width + pos / PAGE];
+  T* dst = pages + (page * PAGE + pos % PAGE) * (rank + rot);
+  float sq = 0.f;
+  for (int c = lane; c < rank; c += 32) {
+    const float v = to_f32(x[c]);
+    sq = fmaf(v, v, sq);
+  }
+  sq = warp_sum(sq);
+  const float inv = 1.0f / sqrtf(sq / (float)rank + eps);
+  for (int c = lane; c < rank; c += 32) dst[c] = from_f32<T>(to_f32(x[c]) * inv * load_param(w, c, w_f32));
+  const int half = rot / 2;
+  for (int p = lane; p < half; p += 32) {
+    const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
+    float sn, cs;
+    sincosf((float)pos * inv_freq[p], &sn, &cs);
+    const float u = to_f32(x[rank + ia]), v = to_f32(x[rank + ib]);
+    dst[rank + ia] = from_f32<T>(u * cs - v * sn);
+    dst[rank + ib] = from_f32<T>(v * cs + u * sn);
+  }
+}
+
+}  // namespace
+
+// Rows of sequences packed one after another (`seq_starts`), each sequence's rows being its last positions
+// (`kv_lens`: its length after the step).  `hp`: heads of a key/value group a block takes together (32 / hp
+// tokens a block).  `v_pages` == `k_pages` and ld_v == ld_k: values are the keys' first dv entries.
+KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out, const void* gate,
+                                      int64_t ld_gate, const int* seq_starts, const int* kv_lens, const int* page_table,
+                                      int table_width, const void* k_pages, const void* v_pages, int n_seqs, int n_heads,
+                                      int n_kv_heads, int dk, int dv, int page_size, int max_new, int hp, float scale,
+                                      float softcap, float slope_span, int window, int keep_first, cudaStream_t stream) {
+  KVAD_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && table_width > 0 && max_new >= 0,
+               "attention (scored): bad sizes seqs=%d heads=%d kv_heads=%d dk=%d dv=%d", n_seqs, n_heads, n_kv_heads, dk, dv);
+  KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention (scored): %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
+  KVAD_REQUIRE(hp >= 1 && hp <= TR, "attention (scored): %d heads a block (1..%d)", hp, TR);
+  KVAD_REQUIRE(keep_first >= 0, "attention (scored): keep_first %d", keep_first);
+  if (dk % 4 != 0 || page_size != PAGE)
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): takes key sizes that are multiples of 4 and pages of %d positions (key size %d, page %d)", PAGE, dk, page_size);
+  KVAD_REQUIRE(n_seqs <= 65535 && n_heads <= 65535, "attention (scored): %d sequences x %d heads are more than one launch takes", n_seqs, n_heads);
+  if (n_seqs == 0 || max_new == 0) return KVAD_OK;
+  const bool alias = v_pages == k_pages;
+  KVAD_REQUIRE(!alias || dv <= dk, "attention (scored): values read from the keys cannot be longer than a key");
+  ScoredArgs a;
+  a.q = q; a.ld_q = ld_q; a.out = out; a.ld_out = ld_out; a.gate = gate; a.ld_gate = ld_gate;
+  a.seq_starts = seq_starts; a.kv_lens = kv_lens; a.page_table = page_table; a.table_width = table_width;
+  a.k_pages = k_pages; a.v_pages = v_pages;
+  a.ld_k = dk; a.k_head_stride = (int64_t)PAGE * dk; a.k_page_stride = (int64_t)n_kv_heads * PAGE * dk;
+  a.ld_v = alias ? dk : dv; a.v_head_stride = (int64_t)PAGE * a.ld_v; a.v_page_stride = (int64_t)n_kv_heads * PAGE * a.ld_v;
+  a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.dk = dk; a.dv = dv; a.hp = hp; a.v_alias = alias ? 1 : 0;
+  a.scale = scale; a.softcap = softcap; a.slope_span = slope_span; a.window = window; a.keep_first = window > 0 ? keep_first : 0;
+  if (dtype == KVAD_DTYPE_F32) return dispatch_scored<float>(a, n_seqs, max_new, stream);
+  if (dtype == KVAD_DTYPE_BF16) return dispatch_scored<__nv_bfloat16>(a, n_seqs, max_new, stream);
+  KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): unknown dtype %d", dtype);
+}
+
+KVAD_EXPORT int kvad_kv_store_blend(int dtype, const void* k_src, int64_t ld_k, const void* v_src, int64_t ld_v, const void* v_other,
+                                    int64_t ld_o, const void* lambda, int lambda_f32, const int* row_seq, const int* row_pos,
+                                    const int* page_table, int table_width, void* k_pages, void* v_pages, int n_rows, int n_kv,
+                                    int dk, int dv, int page_size, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_kv > 0 && dk > 0 && dv > 0 && table_width > 0, "kv_store_blend: bad sizes rows=%d kv_heads=%d dk=%d dv=%d", n_rows, n_kv, dk, dv);
+  KVAD_REQUIRE(page_size == PAGE, "kv_store_blend: pages of %d positions, not %d", PAGE, page_size);
+  KVAD_REQUIRE(v_other == nullptr || lambda != nullptr, "kv_store_blend: a blend needs its weight");
+  if (n_rows == 0) return KVAD_OK;
+  const int64_t total = (int64_t)n_rows * n_kv * (dk + dv);
+  const int threads = 256;
+  const int64_t want = (total + threads - 1) / threads;
+  dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16)), block(threads);
+#define KVAD_ST(T)                                                                                                              \
+  kvad_launch(kv_store_blend_kernel<T>, grid, block, 0, stream, (const T*)k_src, ld_k, (const T*)v_src, ld_v, (const T*)v_other, ld_o, \
+              lambda, lambda_f32, row_seq, row_pos, page_table, table_width, (T*)k_pages, (T*)v_pages, n_rows, n_kv, dk, dv)
+  if (dtype == KVAD_DTYPE_F32) KVAD_ST(float);
+  else if (dtype == KVAD_DTYPE_BF16) KVAD_ST(__nv_bfloat16);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "kv_store_blend: unknown dtype %d", dtype);
+#undef KVAD_ST
+  KVAD_CHECK_LAUNCH("kv_store_blend");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_latent_store(int dtype, const void* src, int64_t ld, const void* w, int w_f32, float eps, const float* inv_freq,
+                                  int interleaved, const int* row_seq, const int* row_pos, const int* page_table, int table_width,
+                                  void* pages, int n_rows, int rank, int rot, int page_size, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && table_width > 0, "latent_store: bad sizes rows=%d rank=%d rot=%d", n_rows, rank, rot);
+  KVAD_REQUIRE(page_size == PAGE, "latent_store: pages of %d positions, not %d", PAGE, page_size);
+  KVAD_REQUIRE(w != nullptr && (rot == 0 || inv_freq != nullptr), "latent_store: needs the norm's weight and the frequencies");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid((n_rows + 3) / 4), block(128);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(latent_store_kernel<float>, grid, block, 0, stream, (const float*)src, ld, w, w_f32, eps, inv_freq, interleaved, row_seq,
+                row_pos, page_table, table_width, (float*)pages, n_rows, rank, rot);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(latent_store_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)src, ld, w, w_f32, eps, inv_freq,
+                interleaved, row_seq, row_pos, page_table, table_width, (__nv_bfloat16*)pages, n_rows, rank, rot);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "latent_store: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("latent_store");
+  return KVAD_OK;
+}
+
+KVAD_DEFINE_LAST_ERROR()

@@ -119,6 +119,9 @@ class StepContext:
         self.seq_slots = meta.seq_slots
         self.want_rows = meta.want_rows
         self.page_tables = meta.tables
+        #: what parts of one step hand to later parts of the same step (a layer's values that later layers blend
+        #: with, a scaled sum still owed to the residual stream); buffers in it come from the arena
+        self.shared: dict = {}
 
     def buffer(self, shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return self.arena.take(shape, dtype or self.dtype)

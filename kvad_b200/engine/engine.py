@@ -168,11 +168,11 @@ class Engine:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: kvad_b200 has no CPU path")
         torch.cuda.set_device(torch.device(device))
-        # compile (first call only) what this model needs, before the weights take time
-        from ..csrc import build
-        build.build_all(libraries_for(tdtype), verbose=True)
         arch, config = load_config(model_dir)
         model = Model(arch.plan(config))
+        # compile (first call only) what this model's parts launch from, and no more, before the weights take time
+        from ..csrc import build
+        build.build_all(libraries_for(tdtype, model.kernel_families()), verbose=True)
         ckpt = Checkpoint.open_dir(model_dir)
         try:
             source = WeightSource(ckpt, ignored_suffixes=model.plan.ignored_suffixes)

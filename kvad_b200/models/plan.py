@@ -93,6 +93,13 @@ class Model:
         """Whether every part's launches depend on a step's shape only (see `Part.graph_safe`)."""
         return all(p.all_graph_safe() for p in self.parts())
 
+    def kernel_families(self) -> list:
+        """The families of kernel libraries this model's parts launch from (`ops.libraries_for`)."""
+        out: list = []
+        for p in self.parts():
+            out.extend(f for f in p.all_kernel_families() if f not in out)
+        return out
+
     # -- weights -------------------------------------------------------------------
     def parts(self):
         return [self.embedding, *self.blocks, self.head]
@@ -113,6 +120,7 @@ class Model:
                 return None
             return source.fetch(name, compute_dtype=dtype, device=device, transpose=transpose, keep_f32=keep_f32)
 
+        fetch.device = device          # for parts that make tables of their own (rotary frequencies)
         for p in self.parts():
             p.load(fetch)
         self.dtype, self.device = dtype, torch.device(device)

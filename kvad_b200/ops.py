@@ -81,6 +81,30 @@ _SIGNATURES = {
         "kvad_attention_decode_pre": [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_int64],
         "kvad_attention_decode_takes_pre": [c_int, c_int, c_int],
     },
+    "norm_rotary": {
+        "kvad_rmsnorm": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_float,
+                         c_void_p],
+        "kvad_residual_rmsnorm": [c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+                                  c_int, c_int, c_float, c_void_p],
+        "kvad_scale_add": [c_void_p, c_void_p, c_float, c_int64, c_void_p],
+        "kvad_rotary": [c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                        c_int, c_int, c_void_p],
+        "kvad_gate_mul": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
+    },
+    "attention_scored": {
+        "kvad_attention_scored": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_float, c_float, c_int, c_int, c_void_p],
+        "kvad_kv_store_blend": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_latent_store": [c_int, c_void_p, c_int64, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                              c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "retention": {
+        "kvad_retention": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_float, c_float, c_int, c_void_p],
+    },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "kvad_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -145,12 +169,25 @@ def lib(name: str) -> ctypes.CDLL:
     return handle
 
 
-def libraries_for(dtype: torch.dtype) -> list[str]:
-    """Which kernel libraries a model of this compute dtype loads."""
-    names = ["rows", "linear_simt", "attention_simt", "sampling"]
-    names += [n for n in ("linear_rows" if dtype == torch.bfloat16 else "linear_rows_f32", "attention_decode") if n in build.sources()]
-    if dtype == torch.bfloat16:
-        names += [n for n in ("linear_tcgen05", "attention_prefill") if n in build.sources()]
+#: kernel libraries by what needs them: every model ("base"), and the families a part names in `Part.kernel_families`
+_FAMILY_LIBRARIES = {
+    "base": {"any": ("rows", "linear_simt", "sampling"), torch.bfloat16: ("linear_rows", "linear_tcgen05"), torch.float32: ("linear_rows_f32",)},
+    "causal_attention": {"any": ("attention_simt", "attention_decode"), torch.bfloat16: ("attention_prefill",), torch.float32: ()},
+    "norm_rotary": {"any": ("norm_rotary",)},
+    "scored_attention": {"any": ("attention_scored",)},
+    "retention": {"any": ("retention",)},
+}
+
+
+def libraries_for(dtype: torch.dtype, families=None) -> list[str]:
+    """Which kernel libraries a model of this compute dtype loads.  `families`: what the model's parts
+    name (`Part.kernel_families`); None: a model of plain causal attention layers."""
+    names: list[str] = []
+    for fam in ["base", *(families if families is not None else ["causal_attention"])]:
+        table = _FAMILY_LIBRARIES[fam]
+        for n in (*table.get("any", ()), *table.get(dtype, ())):
+            if n in build.sources() and n not in names:
+                names.append(n)
     return names
 
 
@@ -562,6 +599,188 @@ class Ops:
         if n_splits > 1 and counters is None:
             global _launches
             _launches += 1          # the merge kernel
+
+    # -- RMS norms, rotary positions, gates ---------------------------------------------
+    def rmsnorm(self, x, weight, eps: float, out, *, unit_offset: bool = False, rows=None, deferred=None) -> None:
+        """out = x / sqrt(mean(x^2) + eps) * w per row (`weight` None: no weight; `unit_offset`: the weight is stored
+        around zero and 1 is added).  `x` is the 32-bit residual stream or activations of the compute dtype, and may
+        be a view of some columns; `rows`: only these rows of x.  `deferred` = (delta, mult): a scaled sum still owed
+        to the stream - the rows are normalised as x + mult * delta; when all rows are walked the sum is written into
+        x and delta is cleared."""
+        _need_cuda(x, weight, out, rows)
+        n, width = out.shape
+        ld_in, ld_out = _rows_view(x, "rmsnorm input"), _rows_view(out, "rmsnorm output")
+        if x.shape[1] != width or out.dtype != self.dtype or x.dtype not in (torch.float32, self.dtype):
+            raise KernelError(f"rmsnorm: input must be float32 or {self.dtype} and as wide as the {self.dtype} output")
+        if rows is None and x.shape[0] < n:
+            raise KernelError("rmsnorm: fewer input rows than output rows")
+        if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n):
+            raise KernelError("rmsnorm: row list must be int32, one per output row")
+        w_f32 = 0
+        if weight is not None:
+            if weight.numel() != width or weight.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("rmsnorm: the weight must have the row's width, float32 or bfloat16")
+            w_f32 = 1 if weight.dtype == torch.float32 else 0
+        h = lib("norm_rotary")
+        if deferred is not None:
+            delta, mult = deferred
+            if (x.dtype != torch.float32 or not x.is_contiguous() or delta.dtype != torch.float32 or not delta.is_contiguous()
+                    or delta.shape != x.shape):
+                raise KernelError("rmsnorm: a deferred sum goes with the contiguous float32 stream and a sum of its shape")
+            _check(h.kvad_residual_rmsnorm(self.code, _ptr(x), _ptr(delta), float(mult), 1 if rows is None else 0, _ptr(rows),
+                                           _ptr(weight), w_f32, int(unit_offset), _ptr(out), ld_out, n, width, float(eps), _stream()), h)
+            return
+        _check(h.kvad_rmsnorm(_code(x.dtype), self.code, _ptr(x), ld_in, _ptr(rows), _ptr(weight), w_f32, int(unit_offset), _ptr(out),
+                              ld_out, n, width, float(eps), _stream()), h)
+
+    def scale_add(self, x, delta, mult: float) -> None:
+        """x += mult * delta; delta = 0 (both the contiguous float32 stream's shape)."""
+        _need_cuda(x, delta)
+        if x.dtype != torch.float32 or delta.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous():
+            raise KernelError("scale_add: needs two contiguous float32 tensors of one shape")
+        h = lib("norm_rotary")
+        _check(h.kvad_scale_add(_ptr(x), _ptr(delta), float(mult), x.numel(), _stream()), h)
+
+    def zero(self, t) -> None:
+        """Clears a contiguous tensor in stream order."""
+        _need_cuda(t)
+        if not t.is_contiguous():
+            raise KernelError("zero: needs a contiguous tensor")
+        h = lib("rows")
+        _check(h.kvad_zero_bytes(_ptr(t), t.numel() * t.element_size(), _stream()), h)
+
+    def rotary(self, src, dst, row_pos, inv_freq, n_heads: int, dims: int, *, interleaved: bool, head_stride_src: int,
+               offset_src: int = 0, head_stride_dst: Optional[int] = None, offset_dst: Optional[int] = None) -> None:
+        """Turns the pairs of `dims` entries of each of `n_heads` heads of every row by the row's position times
+        `inv_freq[pair]` (32-bit angles): head h's entries start at column h * head_stride + offset.  `dst` may be
+        `src` (in place) or another buffer (a copy that turns).  `interleaved`: pairs (2i, 2i+1), else (i, i + dims/2)."""
+        _need_cuda(src, dst, row_pos, inv_freq)
+        ld_s, ld_d = _rows_view(src, "rotary input"), _rows_view(dst, "rotary output")
+        hs_d = head_stride_src if head_stride_dst is None else head_stride_dst
+        off_d = offset_src if offset_dst is None else offset_dst
+        n = src.shape[0]
+        if (src.dtype != self.dtype or dst.dtype != self.dtype or dst.shape[0] != n or inv_freq.dtype != torch.float32
+                or inv_freq.numel() < dims // 2 or row_pos.dtype != torch.int32 or row_pos.numel() < n):
+            raise KernelError("rotary: needs rows of the compute dtype, int32 positions and float32 frequencies, one per pair")
+        if ((n_heads - 1) * head_stride_src + offset_src + dims > src.shape[1] or (n_heads - 1) * hs_d + off_d + dims > dst.shape[1]):
+            raise KernelError("rotary: the heads do not fit the rows")
+        h = lib("norm_rotary")
+        _check(h.kvad_rotary(self.code, _ptr(src), ld_s, int(head_stride_src), int(offset_src), _ptr(dst), ld_d, int(hs_d), int(off_d),
+                             _ptr(row_pos), _ptr(inv_freq), n, int(n_heads), int(dims), int(bool(interleaved)), _stream()), h)
+
+    GATES = {"silu": 0, "sigmoid": 1}
+
+    def gate_mul(self, gate, value, out, act: str = "silu") -> None:
+        """out = act(gate) * value, element by element (`gate`, `value`: views of equal shape, 32-bit arithmetic)."""
+        _need_cuda(gate, value, out)
+        ld_a, ld_b, ld_o = _rows_view(gate, "gate"), _rows_view(value, "gated values"), _rows_view(out, "gate_mul output")
+        if gate.shape != value.shape or out.shape != gate.shape or {gate.dtype, value.dtype, out.dtype} != {self.dtype}:
+            raise KernelError(f"gate_mul: needs three {self.dtype} tensors of one shape")
+        h = lib("norm_rotary")
+        _check(h.kvad_gate_mul(self.code, _ptr(gate), ld_a, _ptr(value), ld_b, _ptr(out), ld_o, gate.shape[0], gate.shape[1],
+                               self.GATES[act], _stream()), h)
+
+    # -- attention with shaped scores ---------------------------------------------------
+    def kv_store_blend(self, k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages, *, v_other=None, blend=None) -> None:
+        """Rows' keys `[rows, kv heads x dk]` and values `[rows, kv heads x dv]` to their places in the pages
+        `[pages, kv heads, 64, dk]` / `[.., dv]`.  With `v_other` (same shape as the values) and `blend` (a scalar in
+        device memory) the stored value is (1 - blend) v + blend v_other."""
+        _need_cuda(k_src, v_src, row_seq, row_pos, page_table, k_pages, v_pages, v_other, blend)
+        ld_k, ld_v = _rows_view(k_src, "keys"), _rows_view(v_src, "values")
+        _, n_kv, page, dk = k_pages.shape
+        dv = v_pages.shape[3]
+        n = k_src.shape[0]
+        if (k_src.shape[1] != n_kv * dk or v_src.shape != (n, n_kv * dv) or v_pages.shape[:3] != k_pages.shape[:3]
+                or {k_src.dtype, v_src.dtype, k_pages.dtype, v_pages.dtype} != {self.dtype} or not k_pages.is_contiguous() or not v_pages.is_contiguous()):
+            raise KernelError(f"kv_store_blend: rows must match the cache's heads and be {self.dtype}")
+        ld_o, lam_f32 = 0, 0
+        if v_other is not None:
+            ld_o = _rows_view(v_other, "the other values")
+            if v_other.shape != v_src.shape or v_other.dtype != self.dtype or blend is None or blend.numel() != 1 or blend.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("kv_store_blend: the other values must have the values' shape, the weight is one float32 or bfloat16 number")
+            lam_f32 = 1 if blend.dtype == torch.float32 else 0
+        h = lib("attention_scored")
+        _check(h.kvad_kv_store_blend(self.code, _ptr(k_src), ld_k, _ptr(v_src), ld_v, _ptr(v_other), ld_o, _ptr(blend if v_other is not None else None),
+                                     lam_f32, _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_pages),
+                                     n, n_kv, dk, dv, page, _stream()), h)
+
+    def latent_store(self, src, weight, eps: float, inv_freq, row_seq, row_pos, page_table, pages, rank: int, rot: int, *,
+                     interleaved: bool) -> None:
+        """Rows `[rows, rank + rot]`: the first `rank` entries RMS-normalised with `weight`, the last `rot` turned by the
+        row's position, stored to pages `[pages, 1, 64, rank + rot]`."""
+        _need_cuda(src, weight, inv_freq, row_seq, row_pos, page_table, pages)
+        ld = _rows_view(src, "latent rows")
+        if (src.shape[1] != rank + rot or pages.shape[1] != 1 or pages.shape[3] != rank + rot or src.dtype != self.dtype or pages.dtype != self.dtype
+                or not pages.is_contiguous() or weight.numel() != rank or weight.dtype not in (torch.float32, torch.bfloat16)):
+            raise KernelError("latent_store: rows and pages must be [.., rank + rot] of the compute dtype, the weight as long as the rank")
+        if rot and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot // 2):
+            raise KernelError("latent_store: needs float32 frequencies, one per pair")
+        h = lib("attention_scored")
+        _check(h.kvad_latent_store(self.code, _ptr(src), ld, _ptr(weight), 1 if weight.dtype == torch.float32 else 0, float(eps), _ptr(inv_freq),
+                                   int(bool(interleaved)), _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(pages),
+                                   src.shape[0], int(rank), int(rot), pages.shape[2], _stream()), h)
+
+    def attention_scored(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages, n_heads: int,
+                         scale: float, *, value_dim: Optional[int] = None, softcap: float = 0.0, slope_span: float = 0.0,
+                         window: int = 0, keep_first: int = 0, gate=None, heads_per_block: int = 1) -> None:
+        """Softmax attention of packed rows (each sequence's rows are its last positions) over the paged cache with
+        shaped scores: s = q.k * scale, capped by `softcap` * tanh(s / softcap) if positive, less slope_h * distance with
+        slope_h = 2^(-slope_span (h+1) / n_heads) if `slope_span` is positive; a row sees the last `window` positions
+        (0: all) and always the first `keep_first`.  `v_pages` None: the values are the first `value_dim` entries of the
+        keys.  `gate`: the output is multiplied by sigmoid(gate).  32-bit arithmetic on the CUDA cores."""
+        _need_cuda(q, out, seq_starts, kv_lens, page_table, k_pages, v_pages, gate)
+        ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
+        _, n_kv, page, dk = k_pages.shape
+        if v_pages is None:
+            dv, v_ptr = int(value_dim or dk), k_pages
+        else:
+            dv, v_ptr = v_pages.shape[3], v_pages
+            if v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != self.dtype or not v_pages.is_contiguous():
+                raise KernelError("attention_scored: the values' pages must match the keys'")
+        if q.shape[1] != n_heads * dk or out.shape != (q.shape[0], n_heads * dv):
+            raise KernelError("attention_scored: queries/output do not match heads x sizes")
+        if {q.dtype, out.dtype, k_pages.dtype} != {self.dtype} or not k_pages.is_contiguous():
+            raise KernelError(f"attention_scored: tensors must be {self.dtype}")
+        ld_g = 0
+        if gate is not None:
+            ld_g = _rows_view(gate, "attention gate")
+            if gate.shape != out.shape or gate.dtype != self.dtype:
+                raise KernelError("attention_scored: the gate must have the output's shape and dtype")
+        h = lib("attention_scored")
+        _check(h.kvad_attention_scored(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(gate), ld_g, _ptr(seq_starts), _ptr(kv_lens),
+                                       _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_ptr), int(n_seqs), int(n_heads), n_kv,
+                                       dk, dv, page, int(max_new), int(heads_per_block), float(scale), float(softcap or 0.0),
+                                       float(slope_span or 0.0), int(window or 0), int(keep_first or 0), _stream()), h)
+
+    # -- retention ------------------------------------------------------------------------
+    def retention(self, q, k, v, out, state, seq_starts, kv_lens, seq_slots, n_seqs: int, decay, n_heads: int, *, inv_freq=None,
+                  rot_dims: int = 0, interleaved: bool = False, k_scale: float = 1.0, gate=None, unit_norm_eps: Optional[float] = None) -> None:
+        """Per sequence and head, over the step's rows in order: S = decay_h S + k v^T, o = S^T q, with q and k turned by
+        position first (`inv_freq`, `rot_dims`), k scaled by `k_scale`; `unit_norm_eps`: o over its root mean square per
+        head; `gate`: times silu(gate).  `state` is `[slots, heads, dk, dv]` float32 and is carried on."""
+        _need_cuda(q, k, v, out, state, seq_starts, kv_lens, seq_slots, decay, inv_freq, gate)
+        ld_q, ld_k, ld_v, ld_o = (_rows_view(t, "retention rows") for t in (q, k, v, out))
+        if state.dim() != 4 or state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1] != n_heads:
+            raise KernelError("retention: the state must be contiguous float32 [slots, heads, dk, dv]")
+        dk, dv = state.shape[2], state.shape[3]
+        n = q.shape[0]
+        if (q.shape[1] != n_heads * dk or k.shape != q.shape or v.shape != (n, n_heads * dv) or out.shape != v.shape
+                or {q.dtype, k.dtype, v.dtype, out.dtype} != {self.dtype}):
+            raise KernelError(f"retention: rows must be {self.dtype} and match heads x sizes of the state")
+        if decay.dtype != torch.float32 or decay.numel() != n_heads:
+            raise KernelError("retention: one float32 decay per head")
+        if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dims // 2):
+            raise KernelError("retention: needs float32 frequencies, one per pair")
+        ld_g = 0
+        if gate is not None:
+            ld_g = _rows_view(gate, "retention gate")
+            if gate.shape != out.shape or gate.dtype != self.dtype:
+                raise KernelError("retention: the gate must have the output's shape and dtype")
+        h = lib("retention")
+        _check(h.kvad_retention(self.code, _ptr(q), ld_q, _ptr(k), ld_k, _ptr(v), ld_v, _ptr(gate), ld_g, _ptr(out), ld_o, _ptr(state),
+                                _ptr(seq_starts), _ptr(kv_lens), _ptr(seq_slots), _ptr(decay), _ptr(inv_freq), int(rot_dims),
+                                int(bool(interleaved)), int(n_seqs), int(n_heads), dk, dv, float(k_scale),
+                                float(unit_norm_eps or 0.0), 0 if unit_norm_eps is None else 1, _stream()), h)
 
     # -- sampling ------------------------------------------------------------------
     ARGMAX_CHUNK = 2048

@@ -22,11 +22,13 @@ import torch
 
 from ..cache.layout import KVNeed
 from .base import Mixer, PartSpec, build_part, register_part
-from .linear import Linear
+from ..weights.source import TensorRequest
+from .linear import FusedLinear, Linear
 
 
 class CausalSelfAttention(Mixer):
     graph_safe = True
+    kernel_families = ("causal_attention",)
 
     def __init__(self, prefix: str, width: int, n_heads: int, head_dim: int, score_scale: float,
                  n_kv_heads: Optional[int] = None, window: Optional[int] = None, bias: bool = True,
@@ -74,6 +76,7 @@ class CausalSelfAttention(Mixer):
         k = qkv[:, self.q_width: self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
         if self.position is not None:
+            ctx.shared["rotary_head_dim"] = self.head_dim
             self.position.rotate(ctx, q, k)
         view = ctx.kv(call.cache)
         mixed = ctx.buffer((n, self.q_width))
@@ -107,4 +110,96 @@ class CausalSelfAttention(Mixer):
                           n_heads, scale, view.window or 0)
 
 
+class ShapedScoreAttention(Mixer):
+    """Softmax attention whose scores are shaped on their way to the softmax, with grouped heads and keys and
+    values of different sizes:
+
+        s_ij = (q_i . k_j) * score_scale;   s <- softcap * tanh(s / softcap)        (if `softcap`)
+        s_ij <- s_ij - slope_h * (i - j),   slope_h = 2^(-slope_span (h+1) / n_heads)   (if `slope_span`)
+        i sees j  iff  j <= i and (i - j < window or j < keep_first)                 (if `window`)
+
+    `value_blend`: "source" - this layer's values are kept for the step (`ctx.shared`) so that later layers can
+    blend with them; "blend" - the values stored and attended over are (1 - b) v + b v_source with b this
+    layer's scalar `blend_name`; a "source" layer's own scalar is asked for and not used.  `gate`: the heads'
+    outputs are multiplied by sigmoid(W_g h) before the output projection.  The four projections are tensors of
+    their own (`[out, in]`, no biases) and run as one product."""
+    graph_safe = True
+    kernel_families = ("scored_attention",)
+
+    def __init__(self, prefix: str, width: int, n_heads: int, key_dim: int, score_scale: float,
+                 n_kv_heads: Optional[int] = None, value_dim: Optional[int] = None, softcap: Optional[float] = None,
+                 slope_span: Optional[float] = None, window: Optional[int] = None, keep_first: int = 0,
+                 value_blend: Optional[str] = None, gate: bool = False, q_name: str = "q", k_name: str = "k",
+                 v_name: str = "v", gate_name: str = "g", out_name: str = "o", blend_name: str = "vmix",
+                 blend_key: str = "first_values"):
+        super().__init__(prefix)
+        self.width, self.n_heads, self.key_dim = int(width), int(n_heads), int(key_dim)
+        self.n_kv_heads = int(n_kv_heads) if n_kv_heads else self.n_heads
+        self.value_dim = int(value_dim) if value_dim else self.key_dim
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads do not divide into {self.n_kv_heads} key/value heads")
+        if self.key_dim % 4:
+            raise ValueError(f"key size {self.key_dim} is not a multiple of 4")
+        if value_blend not in (None, "source", "blend"):
+            raise ValueError("value_blend is None, `source` or `blend`")
+        self.score_scale = float(score_scale)
+        self.softcap = float(softcap) if softcap else 0.0
+        self.slope_span = float(slope_span) if slope_span else 0.0
+        self.window = int(window) if window else None
+        self.keep_first = int(keep_first or 0) if self.window else 0
+        self.value_blend, self.blend_name, self.blend_key, self.gated = value_blend, blend_name, blend_key, bool(gate)
+        self.q_width, self.k_width = self.n_heads * self.key_dim, self.n_kv_heads * self.key_dim
+        self.v_width, self.o_width = self.n_kv_heads * self.value_dim, self.n_heads * self.value_dim
+        maps = [(q_name, self.q_width), (k_name, self.k_width), (v_name, self.v_width)]
+        if self.gated:
+            maps.append((gate_name, self.o_width))
+        self.proj = FusedLinear(prefix, self.width, maps)
+        self.out = Linear(prefix + out_name, self.o_width, self.width, bias=False, weight_name="")
+        self.blend = None
+        group = self.n_heads // self.n_kv_heads
+        self.heads_per_block = max(d for d in (1, 2, 4) if group % d == 0)      # prompts; single-token rows take the whole group
+
+    def children(self):
+        return [self.proj, self.out]
+
+    def own_requests(self):
+        return [TensorRequest(self.prefix + self.blend_name, ())] if self.value_blend else []
+
+    def load_own(self, fetch):
+        if self.value_blend:
+            self.blend = fetch(self.prefix + self.blend_name, keep_f32=True).reshape(1)
+
+    def own_tensors(self):
+        return [self.blend] if self.blend is not None else []
+
+    def cache_need(self):
+        return KVNeed(self.n_kv_heads, self.key_dim, self.window, value_dim=self.value_dim, keep_first=self.keep_first)
+
+    def forward(self, ctx, h, residual, call):
+        n, ops, b = h.shape[0], ctx.ops, ctx.batch
+        buf = ctx.buffer((n, self.proj.out_features))
+        self.proj.forward(ctx, h, buf)
+        q, k, v = (buf[:, self.proj.columns(i)] for i in range(3))
+        gate = buf[:, self.proj.columns(3)] if self.gated else None
+        view = ctx.kv(call.cache)
+        other = None
+        if self.value_blend == "source":
+            ctx.shared[self.blend_key] = v
+        elif self.value_blend == "blend":
+            other = ctx.shared.get(self.blend_key)
+            if other is None or other.shape != v.shape:
+                raise ValueError("value blending: no layer before this one has left values of this shape")
+        if call.writes_cache:
+            ops.kv_store_blend(k, v, ctx.row_seq, ctx.row_pos, view.page_table, view.k_pages, view.v_pages,
+                               v_other=other, blend=self.blend if other is not None else None)
+        mixed = ctx.buffer((n, self.o_width))
+        group = self.n_heads // self.n_kv_heads
+        ops.attention_scored(q, mixed, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
+                             view.v_pages, self.n_heads, self.score_scale, softcap=self.softcap, slope_span=self.slope_span,
+                             window=self.window or 0, keep_first=self.keep_first, gate=gate,
+                             heads_per_block=min(group, 32) if b.is_decode else self.heads_per_block)
+        self.out.forward(ctx, mixed, residual, "residual")
+
+
 register_part("mixer", "causal_attention", CausalSelfAttention)
+register_part("mixer", "shaped_score_attention", ShapedScoreAttention)

@@ -84,6 +84,9 @@ class Part:
     #: positions, lengths or slot ids.  Steps of a model whose parts all say so are captured as CUDA
     #: graphs and replayed.  A part that loops over host data leaves this False and runs kernel by kernel.
     graph_safe = False
+    #: families of kernel libraries the part's launches come from (`ops.libraries_for`); a model compiles
+    #: and loads what its parts name and the libraries every model needs, nothing else
+    kernel_families: tuple = ()
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
@@ -93,6 +96,12 @@ class Part:
 
     def children(self) -> list["Part"]:
         return []
+
+    def all_kernel_families(self) -> list:
+        out = list(self.kernel_families)
+        for c in self.children():
+            out.extend(f for f in c.all_kernel_families() if f not in out)
+        return out
 
     def own_requests(self) -> list[TensorRequest]:
         return []

@@ -57,7 +57,7 @@ class LMHead(Part):
 
     def __init__(self, prefix: str, vocab_size: int, width: int, norm: PartSpec, tied: bool,
                  norm_name: str = "ln_f.", name: str = "lm_head.", bias: bool = False,
-                 embedding: Optional[TokenEmbedding] = None):
+                 embedding: Optional[TokenEmbedding] = None, weight_name: str = "weight"):
         super().__init__(prefix)
         self.vocab_size, self.width, self.tied = int(vocab_size), int(width), bool(tied)
         self.norm = build_part("norm", norm, prefix + norm_name)
@@ -66,8 +66,8 @@ class LMHead(Part):
             raise ValueError("a tied head needs the embedding it is tied to")
         # an untied head may bring a bias; a tied one never reads `lm_head.*`
         self.proj = Linear(prefix + name, self.width, self.vocab_size, bias=(bias and not self.tied),
-                           bias_optional=True, has_weight=not self.tied)
-        self.skipped = [prefix + name + "weight", prefix + name + "bias"] if self.tied else []
+                           bias_optional=True, has_weight=not self.tied, weight_name=weight_name)
+        self.skipped = [prefix + name + weight_name, prefix + name + "bias"] if self.tied else []
 
     def children(self):
         return [self.norm, self.proj]
@@ -77,6 +77,9 @@ class LMHead(Part):
         logits = ctx.buffer((n, self.vocab_size), torch.float32)
         if n == 0:
             return logits
+        if "deferred_residual" in ctx.shared and not getattr(self.norm, "takes_deferred", False):
+            from .block import flush_deferred
+            flush_deferred(ctx)
         h = self.norm.forward(ctx, x, rows=ctx.want_rows, n_rows=n)
         if self.tied:
             self.proj.weight = self.embedding.weight

@@ -8,7 +8,7 @@ product's epilogue, bias and the residual sum in the second's.
 from __future__ import annotations
 
 from .base import FeedForward, register_part
-from .linear import Linear
+from .linear import FusedLinear, Linear
 
 ACTIVATIONS = {"gelu_tanh": "gelu_tanh", "gelu_erf": "gelu_erf"}
 
@@ -34,4 +34,32 @@ class DenseMLP(FeedForward):
         self.down.forward(ctx, hid, residual, "residual")
 
 
+class GatedMLP(FeedForward):
+    """down(act(gate h) * (up h)), no biases; `gate` and `up` are tensors of their own and run as one product,
+    the activation and the multiplication as one row-wise kernel, the residual sum in `down`'s epilogue."""
+    graph_safe = True
+    kernel_families = ("norm_rotary",)
+
+    def __init__(self, prefix: str, width: int, hidden: int, activation: str = "silu", gate_name: str = "gate",
+                 up_name: str = "up", down_name: str = "down"):
+        super().__init__(prefix)
+        if activation not in ("silu", "sigmoid"):
+            raise ValueError(f"gated_mlp has no activation `{activation}`; it has silu and sigmoid")
+        self.width, self.hidden, self.activation = int(width), int(hidden), activation
+        self.gate_up = FusedLinear(prefix, self.width, [(gate_name, self.hidden), (up_name, self.hidden)])
+        self.down = Linear(prefix + down_name, self.hidden, self.width, bias=False, weight_name="")
+
+    def children(self):
+        return [self.gate_up, self.down]
+
+    def forward(self, ctx, h, residual):
+        n = h.shape[0]
+        both = ctx.buffer((n, 2 * self.hidden))
+        self.gate_up.forward(ctx, h, both)
+        hid = ctx.buffer((n, self.hidden))
+        ctx.ops.gate_mul(both[:, :self.hidden], both[:, self.hidden:], hid, self.activation)
+        self.down.forward(ctx, hid, residual, "residual")
+
+
 register_part("feed_forward", "dense_mlp", DenseMLP)
+register_part("feed_forward", "gated_mlp", GatedMLP)

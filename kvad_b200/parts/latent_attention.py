@@ -1,0 +1,111 @@
+"""Latent attention as a mixer: queries and keys/values go through low-rank latents, and only the
+key/value latent and one rotated key part are cached.
+
+    c_q = norm(W_dq h);  q = W_uq c_q, head by head [nope_dim unrotated | rot_dim rotated]
+    W_dkv h = [kv_rank | rot_dim]:  c = norm(first kv_rank),  k_r = rotate(last rot_dim)   (one for all heads)
+    per head: k_n = W_uk c, v = W_uv c;  s_ij = (q_n . k_n + q_r . k_r) * score_scale;  window;  softmax;  W_o
+
+The cache holds [c | k_r] per position: one "head" of kv_rank + rot_dim entries and no values.  The
+keys and values of the heads are never rebuilt: q_n . (W_uk c) = (W_uk^T q_n) . c, so each head's query is
+carried into the latent's space (one small product a head), attention runs with ONE shared key [c | k_r]
+and the latent c itself as the value, and W_uv is applied to the attended latent (one small product a
+head) before the output projection.  Prompts and single-token rows take the same road.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..cache.layout import KVNeed
+from .base import Mixer, PartSpec, build_part, register_part
+from .linear import FusedLinear, Linear
+from ..weights.source import TensorRequest
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+    kernel_families = ("scored_attention", "norm_rotary")
+
+    def __init__(self, prefix: str, width: int, n_heads: int, nope_dim: int, rot_dim: int, value_dim: int, q_rank: int,
+                 kv_rank: int, score_scale: float, norm_eps: float, position: PartSpec, window: Optional[int] = None,
+                 dq_name: str = "dq", dq_norm_name: str = "dq.norm", uq_name: str = "uq", dkv_name: str = "dkv",
+                 dkv_norm_name: str = "dkv.norm", uk_name: str = "uk", uv_name: str = "uv", out_name: str = "o"):
+        super().__init__(prefix)
+        self.width, self.n_heads = int(width), int(n_heads)
+        self.nope_dim, self.rot_dim, self.value_dim = int(nope_dim), int(rot_dim), int(value_dim)
+        self.q_rank, self.kv_rank = int(q_rank), int(kv_rank)
+        self.score_scale, self.norm_eps = float(score_scale), float(norm_eps)
+        self.window = int(window) if window else None
+        self.q_dim = self.nope_dim + self.rot_dim              # a head of the query as the checkpoint has it
+        self.key_dim = self.kv_rank + self.rot_dim             # a cached row, and a head of the carried query
+        if self.key_dim % 4:
+            raise ValueError(f"latent attention: kv_rank + rot_dim = {self.key_dim} is not a multiple of 4")
+        self.down = FusedLinear(prefix, self.width, [(dq_name, self.q_rank), (dkv_name, self.key_dim)])
+        self.up_q = Linear(prefix + uq_name, self.q_rank, self.n_heads * self.q_dim, bias=False, weight_name="")
+        self.out = Linear(prefix + out_name, self.n_heads * self.value_dim, self.width, bias=False, weight_name="")
+        self.position = build_part("position", position, prefix)
+        if self.position.dims != self.rot_dim:
+            raise ValueError("latent attention: the rotary encoding turns exactly the rotated part")
+        self.names = dict(dq_norm=dq_norm_name, dkv_norm=dkv_norm_name, uk=uk_name, uv=uv_name)
+        self.q_norm = self.kv_norm = None
+        self.uk_t: list = []     # per head W_uk_h^T [kv_rank, nope_dim]
+        self.uv: list = []       # per head W_uv_h   [value_dim, kv_rank]
+        self._uk = self._uv = None
+
+    def children(self):
+        return [self.down, self.up_q, self.out, self.position]
+
+    def own_requests(self):
+        p, n = self.prefix, self.names
+        return [TensorRequest(p + n["dq_norm"], (self.q_rank,)), TensorRequest(p + n["dkv_norm"], (self.kv_rank,)),
+                TensorRequest(p + n["uk"], (self.n_heads * self.nope_dim, self.kv_rank)),
+                TensorRequest(p + n["uv"], (self.n_heads * self.value_dim, self.kv_rank))]
+
+    def load_own(self, fetch):
+        p, n = self.prefix, self.names
+        self.q_norm = fetch(p + n["dq_norm"], keep_f32=True)
+        self.kv_norm = fetch(p + n["dkv_norm"], keep_f32=True)
+        uk = fetch(p + n["uk"]).view(self.n_heads, self.nope_dim, self.kv_rank)
+        self._uk = uk.transpose(1, 2).contiguous()             # [heads, kv_rank, nope_dim]: head h's map into the latent's space
+        self._uv = fetch(p + n["uv"]).view(self.n_heads, self.value_dim, self.kv_rank).contiguous()
+        self.uk_t = [self._uk[h] for h in range(self.n_heads)]
+        self.uv = [self._uv[h] for h in range(self.n_heads)]
+
+    def own_tensors(self):
+        return [t for t in (self.q_norm, self.kv_norm, self._uk, self._uv) if t is not None]
+
+    def cache_need(self):
+        return KVNeed(1, self.key_dim, self.window, value_dim=0)
+
+    def forward(self, ctx, h, residual, call):
+        n, ops, b, H = h.shape[0], ctx.ops, ctx.batch, self.n_heads
+        down = ctx.buffer((n, self.down.out_features))
+        self.down.forward(ctx, h, down)
+        view = ctx.kv(call.cache)
+        if call.writes_cache:
+            ops.latent_store(down[:, self.down.columns(1)], self.kv_norm, self.norm_eps, self.position.inv_freq, ctx.row_seq,
+                             ctx.row_pos, view.page_table, view.k_pages, self.kv_rank, self.rot_dim,
+                             interleaved=self.position.interleaved)
+        cq = ctx.buffer((n, self.q_rank))
+        ops.rmsnorm(down[:, self.down.columns(0)], self.q_norm, self.norm_eps, cq)
+        q = ctx.buffer((n, H * self.q_dim))
+        self.up_q.forward(ctx, cq, q)
+        # each head's query in the latent's space: [W_uk_h^T q_n | rotate(q_r)]
+        ql = ctx.buffer((n, H * self.key_dim))
+        for hd in range(H):
+            ops.linear(q[:, hd * self.q_dim: hd * self.q_dim + self.nope_dim], self.uk_t[hd], None,
+                       ql[:, hd * self.key_dim: hd * self.key_dim + self.kv_rank])
+        self.position.rotate_heads(ctx, q, ql, H, self.q_dim, self.nope_dim, self.key_dim, self.kv_rank)
+        attended = ctx.buffer((n, H * self.kv_rank))
+        ops.attention_scored(ql, attended, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
+                             None, H, self.score_scale, value_dim=self.kv_rank, window=self.window or 0,
+                             heads_per_block=min(H, 32) if b.is_decode else max(d for d in (1, 2, 4) if H % d == 0))
+        mixed = ctx.buffer((n, H * self.value_dim))
+        for hd in range(H):
+            ops.linear(attended[:, hd * self.kv_rank:(hd + 1) * self.kv_rank], self.uv[hd], None,
+                       mixed[:, hd * self.value_dim:(hd + 1) * self.value_dim])
+        self.out.forward(ctx, mixed, residual, "residual")
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -21,13 +21,15 @@ class Linear(Part):
 
     def __init__(self, prefix: str, in_features: int, out_features: int, *, bias: bool = True,
                  stored: str = "out_in", shared_weight: Optional[torch.Tensor] = None,
-                 bias_optional: bool = False, has_weight: bool = True):
+                 bias_optional: bool = False, has_weight: bool = True, weight_name: str = "weight",
+                 bias_name: str = "bias"):
         super().__init__(prefix)
         if stored not in ("out_in", "in_out"):
             raise ValueError("stored must be `out_in` or `in_out`")
         self.in_features, self.out_features = int(in_features), int(out_features)
         self.has_bias, self.bias_optional, self.stored = bias, bias_optional, stored
         self.has_weight = has_weight            # False: the weight is lent by another part (a tied head)
+        self.weight_name, self.bias_name = weight_name, bias_name      # tensor = prefix + name ("" : the prefix is the name)
         self.weight: Optional[torch.Tensor] = shared_weight
         self.bias: Optional[torch.Tensor] = None
 
@@ -35,16 +37,16 @@ class Linear(Part):
         out = []
         if self.has_weight:
             shape = (self.out_features, self.in_features) if self.stored == "out_in" else (self.in_features, self.out_features)
-            out.append(TensorRequest(self.prefix + "weight", shape))
+            out.append(TensorRequest(self.prefix + self.weight_name, shape))
         if self.has_bias:
-            out.append(TensorRequest(self.prefix + "bias", (self.out_features,), optional=self.bias_optional))
+            out.append(TensorRequest(self.prefix + self.bias_name, (self.out_features,), optional=self.bias_optional))
         return out
 
     def load_own(self, fetch):
         if self.has_weight:
-            self.weight = fetch(self.prefix + "weight", transpose=self.stored == "in_out")
+            self.weight = fetch(self.prefix + self.weight_name, transpose=self.stored == "in_out")
         if self.has_bias:
-            self.bias = fetch(self.prefix + "bias", keep_f32=True, optional=self.bias_optional)
+            self.bias = fetch(self.prefix + self.bias_name, keep_f32=True, optional=self.bias_optional)
 
     def own_tensors(self):
         return [t for t in ((self.weight if self.has_weight else None), self.bias) if t is not None]
@@ -52,4 +54,36 @@ class Linear(Part):
     def forward(self, ctx, a, out: torch.Tensor, epilogue: str = "store") -> torch.Tensor:
         """out = epilogue(a . W^T + b)."""
         ctx.ops.linear(a, self.weight, self.bias, out, epilogue)
+        return out
+
+
+class FusedLinear(Part):
+    """Several bias-free linear maps of one input, stored as tensors of their own (`[out, in]` each) and held
+    as ONE matrix, rows one map after another: one product gives all of them, each a range of columns of the
+    output (`columns(i)`)."""
+    graph_safe = True
+
+    def __init__(self, prefix: str, in_features: int, parts):
+        super().__init__(prefix)
+        self.in_features = int(in_features)
+        self.names = [str(n) for n, _ in parts]
+        self.sizes = [int(o) for _, o in parts]
+        self.out_features = sum(self.sizes)
+        self.weight: Optional[torch.Tensor] = None
+
+    def own_requests(self):
+        return [TensorRequest(self.prefix + n, (o, self.in_features)) for n, o in zip(self.names, self.sizes)]
+
+    def load_own(self, fetch):
+        self.weight = torch.cat([fetch(self.prefix + n) for n in self.names], dim=0).contiguous()
+
+    def own_tensors(self):
+        return [self.weight]
+
+    def columns(self, i: int) -> slice:
+        lo = sum(self.sizes[:i])
+        return slice(lo, lo + self.sizes[i])
+
+    def forward(self, ctx, a, out: torch.Tensor, epilogue: str = "store") -> torch.Tensor:
+        ctx.ops.linear(a, self.weight, None, out, epilogue)
         return out

@@ -1,9 +1,13 @@
-"""Norms.  `layernorm`: centre, scale to unit variance (biased, eps inside the
+"""Norms.  `rmsnorm`: x / sqrt(mean(x^2) + eps) times a weight, which may be stored around zero
+(`unit_offset`: 1 is added) or be absent; it also takes up a scaled sum that a block before it still
+owes to the residual stream (see `ParallelBlock`).  `layernorm`: centre, scale to unit variance (biased, eps inside the
 root), then gain and bias - bisand/kvad's `layer_norm`
 (crates/llm/src/tensor.rs:245-255).  Computed in 32-bit from the 32-bit
 residual stream; gain and bias stay in 32-bit if the checkpoint stores them so.
 """
 from __future__ import annotations
+
+import torch
 
 from ..weights.source import TensorRequest
 from .base import Norm, register_part
@@ -42,4 +46,45 @@ class LayerNorm(Norm):
         return out
 
 
+class RMSNorm(Norm):
+    graph_safe = True
+    kernel_families = ("norm_rotary",)
+    #: a scaled sum that a block has left in `ctx.shared["deferred_residual"]` is folded in by this norm
+    takes_deferred = True
+
+    def __init__(self, prefix: str, width: int, eps: float, unit_offset: bool = False, name: str = "weight",
+                 has_weight: bool = True):
+        super().__init__(prefix)
+        self.width, self.eps, self.unit_offset = int(width), float(eps), bool(unit_offset)
+        self.name, self.has_weight = name, bool(has_weight)
+        self.weight = None
+
+    def own_requests(self):
+        return [TensorRequest(self.prefix + self.name, (self.width,))] if self.has_weight else []
+
+    def load_own(self, fetch):
+        if self.has_weight:
+            self.weight = fetch(self.prefix + self.name, keep_f32=True)
+
+    def own_tensors(self):
+        return [self.weight] if self.weight is not None else []
+
+    def forward(self, ctx, x, rows=None, n_rows=None):
+        n = n_rows if n_rows is not None else (x.shape[0] if rows is None else rows.numel())
+        out = ctx.buffer((n, self.width))
+        deferred = ctx.shared.get("deferred_residual") if x.dtype == torch.float32 else None
+        if deferred is not None and deferred[0] is not x:
+            deferred = None
+        if deferred is not None:
+            _, delta, mult = deferred
+            ctx.ops.rmsnorm(x[:ctx.n_rows], self.weight, self.eps, out, unit_offset=self.unit_offset, rows=rows,
+                            deferred=(delta, mult))
+            if rows is None:                      # the sum is in the stream now
+                ctx.shared.pop("deferred_residual")
+        else:
+            ctx.ops.rmsnorm(x, self.weight, self.eps, out, unit_offset=self.unit_offset, rows=rows)
+        return out
+
+
 register_part("norm", "layernorm", LayerNorm)
+register_part("norm", "rmsnorm", RMSNorm)

@@ -3,7 +3,10 @@
 `learned_absolute`: one learned vector per position, added to the token
 embedding at the bottom of the model (bisand/kvad: `wpe`,
 crates/llm/src/model/gpt2.rs:71-75, 200-213).  It bounds a sequence's length:
-there is no row past the table's end.  `none`: no position information of its
+there is no row past the table's end.  `rotary`: pairs of a head's first `dims` entries are turned by position times
+base^(-2i/dims), pair i being entries (i, i + dims/2) (`layout="half"`) or (2i, 2i+1)
+(`layout="interleaved"`); angles and sines are 32-bit.  A mixer either calls `rotate` on its
+queries and keys or hands `inv_freq` to a kernel that turns them itself.  `none`: no position information of its
 own (a mixer may still bring one).
 """
 from __future__ import annotations
@@ -33,6 +36,51 @@ class LearnedAbsolute(PositionEncoding):
         return self.weight
 
 
+class Rotary(PositionEncoding):
+    graph_safe = True
+    kernel_families = ("norm_rotary",)
+
+    def __init__(self, prefix: str = "", dims: int = 0, base: float = 10000.0, layout: str = "half"):
+        super().__init__(prefix)
+        if layout not in ("half", "interleaved"):
+            raise ValueError("a rotary layout is `half` or `interleaved`")
+        if dims <= 0 or dims % 2:
+            raise ValueError(f"a rotary encoding turns an even, positive number of entries, not {dims}")
+        self.dims, self.base, self.layout = int(dims), float(base), layout
+        self.inv_freq = None
+
+    @property
+    def interleaved(self) -> bool:
+        return self.layout == "interleaved"
+
+    def load_own(self, fetch):
+        import numpy as np
+        import torch
+        # (the frequencies in 64-bit, rounded once; angles are position x frequency in 32-bit)
+        f = np.float64(self.base) ** (-2.0 * np.arange(self.dims // 2, dtype=np.float64) / self.dims)
+        self.inv_freq = torch.from_numpy(f.astype(np.float32)).to(self._device(fetch))
+
+    @staticmethod
+    def _device(fetch):
+        return getattr(fetch, "device", "cuda")
+
+    def rotate_heads(self, ctx, src, dst, n_heads: int, head_stride_src: int, offset_src: int = 0,
+                     head_stride_dst=None, offset_dst=None) -> None:
+        """Turns `dims` entries of each head of every row of `src` into `dst` (which may be `src`)."""
+        ctx.ops.rotary(src, dst, ctx.row_pos, self.inv_freq, n_heads, self.dims, interleaved=self.interleaved,
+                       head_stride_src=head_stride_src, offset_src=offset_src, head_stride_dst=head_stride_dst,
+                       offset_dst=offset_dst)
+
+    def rotate(self, ctx, q, k) -> None:
+        """In place on queries and keys whose heads are as long as `head_dim` = their width / heads; used by
+        a mixer that gives its head size as `q.shape[1] // n_heads` through `ctx.shared["rotary_head_dim"]`."""
+        hd = ctx.shared.get("rotary_head_dim")
+        if not hd:
+            raise ValueError("rotary: the mixer must say its head size")
+        self.rotate_heads(ctx, q, q, q.shape[1] // hd, hd)
+        self.rotate_heads(ctx, k, k, k.shape[1] // hd, hd)
+
+
 class NoPositions(PositionEncoding):
     graph_safe = True
 
@@ -42,3 +90,4 @@ class NoPositions(PositionEncoding):
 
 register_part("position", "learned_absolute", LearnedAbsolute)
 register_part("position", "none", NoPositions)
+register_part("position", "rotary", Rotary)
