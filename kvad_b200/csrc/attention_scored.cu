@@ -47,9 +47,9 @@ template <typename T, int KPL, int DPL>
 __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredArgs a) {
   constexpr int TK = 32 * KPL;
   extern __shared__ float smem[];
-  const int dk = a.dk, dv = a.dv, ldks = dk + 1, ldvs = a.v_alias ? ldks : dv;
-  float* Qs = smem;                                   // [TR][dk]
-  float* Ks = Qs + TR * dk;                           // [TK][dk + 1]
+  const int dk = a.dk, dv = a.dv, dkp = (dk + 3) & ~3, ldks = dkp + 1, ldvs = a.v_alias ? ldks : dv;   // (keys padded with zeros to fours)
+  float* Qs = smem;                                   // [TR][dkp]
+  float* Ks = Qs + TR * dkp;                          // [TK][dkp + 1]
   float* Vs = a.v_alias ? Ks : Ks + TK * ldks;        // [TK][ldvs]
   float* Ps = a.v_alias ? Ks + TK * ldks : Vs + TK * dv;   // [TR][TK]
   pdl_launch_dependents();
@@ -66,9 +66,9 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* q = (const T*)a.q;
 
-  for (int i = tid; i < TR * dk; i += THREADS) {
-    const int r = i / dk, d = i - r * dk, ti = r / hp, hi = r - ti * hp;
-    Qs[i] = (ti < n_tok && hi < n_h) ? to_f32(q[(int64_t)(start + tok0 + ti) * a.ld_q + (int64_t)(h0 + hi) * dk + d]) : 0.f;
+  for (int i = tid; i < TR * dkp; i += THREADS) {
+    const int r = i / dkp, d = i - r * dkp, ti = r / hp, hi = r - ti * hp;
+    Qs[i] = (ti < n_tok && hi < n_h && d < dk) ? to_f32(q[(int64_t)(start + tok0 + ti) * a.ld_q + (int64_t)(h0 + hi) * dk + d]) : 0.f;
   }
   // what each of the warp's pairs is: its position, whether it exists, its head's slope
   int row_pos[RPW];
@@ -98,9 +98,9 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
     __syncthreads();                                                    // the tile before has been used up (and Qs is written)
     const int page = pages[key0 / PAGE], in_page = key0 % PAGE;
     const T* kt = kp + (int64_t)page * a.k_page_stride + (int64_t)kvh * a.k_head_stride + (int64_t)in_page * a.ld_k;
-    for (int i = tid; i < TK * dk; i += THREADS) {
-      const int k = i / dk, d = i - k * dk;
-      Ks[k * ldks + d] = key0 + k <= last_pos ? to_f32(kt[(int64_t)k * a.ld_k + d]) : 0.f;   // (a place no row sees yet may hold anything)
+    for (int i = tid; i < TK * dkp; i += THREADS) {
+      const int k = i / dkp, d = i - k * dkp;
+      Ks[k * ldks + d] = (key0 + k <= last_pos && d < dk) ? to_f32(kt[(int64_t)k * a.ld_k + d]) : 0.f;   // (a place no row sees yet may hold anything)
     }
     if (!a.v_alias) {
       const T* vt = vp + (int64_t)page * a.v_page_stride + (int64_t)kvh * a.v_head_stride + (int64_t)in_page * a.ld_v;
@@ -115,8 +115,8 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
     for (int r = 0; r < RPW; ++r)
 #pragma unroll
       for (int j = 0; j < KPL; ++j) sc[r][j] = 0.f;
-    const float* qw = Qs + warp * RPW * dk;
-    for (int d = 0; d < dk; d += 4) {
+    const float* qw = Qs + warp * RPW * dkp;
+    for (int d = 0; d < dkp; d += 4) {
       float kv[KPL][4];
 #pragma unroll
       for (int j = 0; j < KPL; ++j) {
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
       }
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        const float4 qv = *reinterpret_cast<const float4*>(qw + r * dk + d);
+        const float4 qv = *reinterpret_cast<const float4*>(qw + r * dkp + d);
 #pragma unroll
         for (int j = 0; j < KPL; ++j)
           sc[r][j] = fmaf(qv.w, kv[j][3], fmaf(qv.z, kv[j][2], fmaf(qv.y, kv[j][1], fmaf(qv.x, kv[j][0], sc[r][j]))));
@@ -219,8 +219,9 @@ int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cud
 template <typename T>
 int dispatch_scored(const ScoredArgs& a, int n_seqs, int max_new, cudaStream_t stream) {
   const size_t limit = 200 * 1024;
+  const size_t dkp = (size_t)((a.dk + 3) & ~3);
   auto need = [&](int tk) {
-    return ((size_t)TR * a.dk + (size_t)tk * (a.dk + 1) + (a.v_alias ? 0 : (size_t)tk * a.dv) + (size_t)TR * tk) * sizeof(float);
+    return ((size_t)TR * dkp + (size_t)tk * (dkp + 1) + (a.v_alias ? 0 : (size_t)tk * a.dv) + (size_t)TR * tk) * sizeof(float);
   };
   const int kpl = need(64) <= limit ? 2 : 1;
   const size_t smem = need(32 * kpl);
@@ -322,8 +323,8 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention (scored): %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
   KVAD_REQUIRE(hp >= 1 && hp <= TR, "attention (scored): %d heads a block (1..%d)", hp, TR);
   KVAD_REQUIRE(keep_first >= 0, "attention (scored): keep_first %d", keep_first);
-  if (dk % 4 != 0 || page_size != PAGE)
-    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): takes key sizes that are multiples of 4 and pages of %d positions (key size %d, page %d)", PAGE, dk, page_size);
+  if (page_size != PAGE)
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): takes pages of %d positions, not %d", PAGE, page_size);
   KVAD_REQUIRE(n_seqs <= 65535 && n_heads <= 65535, "attention (scored): %d sequences x %d heads are more than one launch takes", n_seqs, n_heads);
   if (n_seqs == 0 || max_new == 0) return KVAD_OK;
   const bool alias = v_pages == k_pages;

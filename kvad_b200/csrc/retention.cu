@@ -37,8 +37,11 @@ struct RetentionArgs {
   int unit_norm;
 };
 
+// (the more state a thread holds, the fewer threads a block may have: registers)
+constexpr int max_threads(int dpt) { return dpt == 16 ? 1024 : (dpt <= 32 ? 512 : 256); }
+
 template <typename T, int DPT>
-__global__ void retention_kernel(const RetentionArgs a) {
+__global__ void __launch_bounds__(max_threads(DPT)) retention_kernel(const RetentionArgs a) {
   extern __shared__ float smem[];
   const int dk = a.dk, dv = a.dv, split = a.split, dkp = split * DPT;
   float* qs = smem;                     // [TB][dkp]
@@ -163,7 +166,7 @@ int dispatch_retention(RetentionArgs& a, int n_seqs, cudaStream_t stream) {
     while (split * dpt < a.dk) split <<= 1;
     if (split > 32) continue;
     const int threads = (a.dv * split + 31) / 32 * 32;
-    if (threads > (dpt == 8 ? 512 : 1024)) continue;
+    if (threads > max_threads(dpt)) continue;
     a.split = split;
     switch (dpt) {
       case 8: return launch_retention<T, 8>(a, n_seqs, threads, stream);
@@ -172,7 +175,7 @@ int dispatch_retention(RetentionArgs& a, int n_seqs, cudaStream_t stream) {
       default: return launch_retention<T, 64>(a, n_seqs, threads, stream);
     }
   }
-  KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "retention: a state of %d x %d a head does not fit a block", a.dk, a.dv);
+  KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "retention: a state of %d x %d a head does not fit a block (up to 128 x 128, or 64 x 256)", a.dk, a.dv);
 }
 
 }  // namespace

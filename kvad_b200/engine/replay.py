@@ -86,12 +86,14 @@ def main(argv=None) -> int:
     p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True, help="folder for <step>.f32 files")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                   help="most tokens live requests hold at any time (room for 128 partly filled pages is added)")
     args = p.parse_args(argv)
 
     from .engine import Engine
 
-    engine = Engine.from_pretrained(args.model, args.dtype, max_tokens=args.max_tokens)
+    # the cache counts whole pages: every live request may leave most of its last page empty
+    from ..cache.pages import PAGE_SIZE
+    engine = Engine.from_pretrained(args.model, args.dtype, max_tokens=args.max_tokens + 128 * PAGE_SIZE)
     print(f"[kvad_b200] {engine.describe()}", file=sys.stderr, flush=True)
     Replayer(engine, args.out).run(sys.stdin)
     return 0

@@ -80,8 +80,6 @@ def read_config(view: JsonView) -> NifulixConfig:
             if heads % kv:
                 raise ConfigError(f"config: {where}: {heads} heads do not divide into {kv} key/value heads")
             _need(m, "scale", where)
-            if dim % 4:
-                raise ConfigError(f"config: {where}: key size {dim} is not a multiple of 4, which the kernels need")
             if m.get("v_mix"):
                 if blend_shape is not None and blend_shape != (kv, vdim):
                     raise ConfigError(f"config: {where}: layers that blend values must have values of one shape")
@@ -100,8 +98,8 @@ def read_config(view: JsonView) -> NifulixConfig:
             rot_dim = _pos_int(m, "rot_dim", where)
             _pos_int(m, "kv_rank", where), _pos_int(m, "q_rank", where), _need(m, "scale", where)
             _need(m.get("rot"), "base", where + " rot")
-            if rot_dim % 2 or (m["kv_rank"] + rot_dim) % 4:
-                raise ConfigError(f"config: {where}: rot_dim must be even and kv_rank + rot_dim a multiple of 4")
+            if rot_dim % 2:
+                raise ConfigError(f"config: {where}: rot_dim must be even")
         mlp = layer.get("mlp")
         if mlp is not None:
             if not isinstance(mlp, dict) or mlp.get("kind") != "dense":

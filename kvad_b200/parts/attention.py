@@ -138,8 +138,6 @@ class ShapedScoreAttention(Mixer):
         self.value_dim = int(value_dim) if value_dim else self.key_dim
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_heads} heads do not divide into {self.n_kv_heads} key/value heads")
-        if self.key_dim % 4:
-            raise ValueError(f"key size {self.key_dim} is not a multiple of 4")
         if value_blend not in (None, "source", "blend"):
             raise ValueError("value_blend is None, `source` or `blend`")
         self.score_scale = float(score_scale)

@@ -39,8 +39,6 @@ class LatentAttention(Mixer):
         self.window = int(window) if window else None
         self.q_dim = self.nope_dim + self.rot_dim              # a head of the query as the checkpoint has it
         self.key_dim = self.kv_rank + self.rot_dim             # a cached row, and a head of the carried query
-        if self.key_dim % 4:
-            raise ValueError(f"latent attention: kv_rank + rot_dim = {self.key_dim} is not a multiple of 4")
         self.down = FusedLinear(prefix, self.width, [(dq_name, self.q_rank), (dkv_name, self.key_dim)])
         self.up_q = Linear(prefix + uq_name, self.q_rank, self.n_heads * self.q_dim, bias=False, weight_name="")
         self.out = Linear(prefix + out_name, self.n_heads * self.value_dim, self.width, bias=False, weight_name="")

@@ -139,8 +139,11 @@ def mix_retention(h, t, p, m, eps, shared):
     n = h.shape[0]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
     pos = np.arange(n)
-    q = rotate((h @ t[p + "q"].T).reshape(n, H, dk), pos, m["rot"]["base"], m["rot"]["dims"], "half")
-    k = rotate((h @ t[p + "k"].T).reshape(n, H, dk), pos, m["rot"]["base"], m["rot"]["dims"], "half") * dk ** -0.5
+    q, k = (h @ t[p + "q"].T).reshape(n, H, dk), (h @ t[p + "k"].T).reshape(n, H, dk)
+    if m.get("rot"):
+        q = rotate(q, pos, m["rot"]["base"], m["rot"]["dims"], "half")
+        k = rotate(k, pos, m["rot"]["base"], m["rot"]["dims"], "half")
+    k = k * dk ** -0.5
     v = (h @ t[p + "v"].T).reshape(n, H, dv)
     out = np.zeros((n, H, dv))
     for hd in range(H):

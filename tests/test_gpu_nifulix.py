@@ -1,0 +1,211 @@
+"""Nifulix through the engine - its step function, cache, state and scheduler - against the plain
+implementation (tests/plain/nifulix_plain.py, float64, whole sequences): whole prompts, token-by-token
+decoding, portions down to two tokens, unequal batches against each request alone, slots and pages that are
+freed and used again, windows that slide over page borders while decoding, the first tokens of a sequence,
+long decoding, and greedy generation through the entry point.  The float32 engine is held to rounding of
+32-bit sums; the bfloat16 engine to the rounding of its stored activations."""
+import numpy as np
+import pytest
+
+from kvad_b200 import Engine, StepEntry, write_random_model
+from tests.conftest import random_tokens, rel_err
+from tests.nifulix_configs import CONFIGS, SEEDS
+from tests.plain.nifulix_plain import PlainNifulix
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+CASES = [(n, d) for n in sorted(CONFIGS) for d in ("float32", "bfloat16")]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {n: write_random_model(str(tmp_path_factory.mktemp("nifulix" + n)), CONFIGS[n], SEEDS[n]) for n in CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def oracle(folders):
+    cache = {}
+
+    def get(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in cache:
+            cache[key] = PlainNifulix(folders[name]).forward(list(tokens))
+        return cache[key]
+    return get
+
+
+@pytest.fixture(scope="module")
+def engine(folders):
+    cache = {}
+
+    def get(name, dtype, max_tokens=2048):
+        if (name, dtype) not in cache:
+            cache[(name, dtype)] = Engine.from_pretrained(folders[name], dtype, max_tokens=max_tokens)
+        return cache[(name, dtype)]
+    return get
+
+
+def close(got, ref, dtype, what=""):
+    e = rel_err(got, ref)
+    assert e < TOL[dtype], (what, e)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_prompts_and_the_residual_stream(engine, oracle, folders, name, dtype):
+    e = engine(name, dtype)
+    assert e.use_graphs                                   # every part's launches depend on the step's shape only
+    vocab = CONFIGS[name]["vocab"]
+    for seed, n in ((1, 1), (2, 2), (3, 63), (4, 64), (5, 65), (6, 300)):
+        toks = random_tokens(seed, n, vocab)
+        s = e.open()
+        got = e.step([StepEntry(s, toks, range(n))]).cpu().numpy()
+        e.close(s)
+        close(got, oracle(name, toks), dtype, n)
+    e.cache.book.check_all_free()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_prompt_then_token_by_token_across_windows_and_pages(engine, oracle, name, dtype):
+    """A prompt, then 150 single tokens: every window of the configuration slides over decoded tokens, over a
+    page border, and the windowed groups give pages back on the way."""
+    e = engine(name, dtype)
+    toks = random_tokens(11, 260, CONFIGS[name]["vocab"])
+    ref = oracle(name, toks)
+    s = e.open()
+    got = e.step([StepEntry(s, toks[:110], [0, 109])]).cpu().numpy()
+    close(got, ref[[0, 109]], dtype)
+    free_at_start = [p.n_free for p in e.cache.book.pools]
+    for p in range(110, 260):
+        got = e.step([StepEntry(s, [toks[p]], [0])]).cpu().numpy()
+        close(got[0], ref[p], dtype, p)
+    windows = e.cache.book.windows
+    for g, w in enumerate(windows):                       # a window shorter than two pages has dropped pages by now
+        if w is not None and w <= 128:
+            assert any(x < 0 for x in e.cache.book.pages[s][g])
+    e.close(s)
+    e.cache.book.check_all_free()
+    assert free_at_start is not None
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("cuts", [[2, 2, 2, 58, 2, 3, 131], [64, 64, 64, 8], [1, 127, 65, 7], [199, 1]])
+def test_portions_of_a_prompt(engine, oracle, name, dtype, cuts):
+    e = engine(name, dtype)
+    toks = random_tokens(21, 200, CONFIGS[name]["vocab"])
+    ref = oracle(name, toks)
+    s, at = e.open(), 0
+    for c in cuts:
+        got = e.step([StepEntry(s, toks[at:at + c], range(c))]).cpu().numpy()
+        close(got, ref[at:at + c], dtype, (cuts, at))
+        at += c
+    e.close(s)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_against_each_alone_and_slots_used_again(engine, oracle, name, dtype):
+    e = engine(name, dtype)
+    vocab = CONFIGS[name]["vocab"]
+    lens = [1, 150, 37, 90]
+    reqs = [random_tokens(30 + i, n + 40, vocab) for i, n in enumerate(lens)]
+    refs = [oracle(name, r) for r in reqs]
+    for rnd in range(2):                                   # the second round takes the slots and pages the first gave back
+        slots = [e.open() for _ in reqs]
+        got = e.step([StepEntry(s, r[:n], [n - 1]) for s, r, n in zip(slots, reqs, lens)]).cpu().numpy()
+        for i, n in enumerate(lens):
+            close(got[i], refs[i][n - 1], dtype, ("prompt", i))
+        live = list(range(len(reqs)))
+        for j in range(40):
+            if j == 10:                                    # a request ends early; the batch goes on without it
+                e.close(slots[2])
+                live.remove(2)
+            if j == 25:
+                e.close(slots[0])
+                live.remove(0)
+            got = e.step([StepEntry(slots[i], [reqs[i][lens[i] + j]], [0]) for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                close(got[row], refs[i][lens[i] + j], dtype, ("decode", rnd, j, i))
+        for i in live:
+            e.close(slots[i])
+        e.cache.book.check_all_free()
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_company_and_cutting_change_nothing_beyond_rounding_in_32_bit(engine, name):
+    """The same position computed alone, in a batch, as part of a whole prompt or decoded: the differences are
+    those of the products' row-count classes (sums in another order), far below the oracle tolerance."""
+    e = engine(name, "float32")
+    vocab = CONFIGS[name]["vocab"]
+    a, b = random_tokens(41, 140, vocab), random_tokens(42, 75, vocab)
+    s = e.open()
+    alone = e.step([StepEntry(s, a, [139])]).cpu().numpy()[0]
+    e.close(s)
+    sa, sb = e.open(), e.open()
+    e.step([StepEntry(sa, a[:100], []), StepEntry(sb, b[:70], [])])
+    e.step([StepEntry(sa, a[100:139], []), StepEntry(sb, b[70:74], [])])
+    both = e.step([StepEntry(sa, [a[139]], [0]), StepEntry(sb, [b[74]], [0])]).cpu().numpy()[0]
+    e.close(sa), e.close(sb)
+    assert rel_err(both, alone) < 3e-6
+
+
+@pytest.mark.parametrize("name,dtype", [("P", "float32"), ("Q", "float32"), ("R", "bfloat16")])
+def test_greedy_generation_through_the_entry_point(engine, folders, name, dtype):
+    e = engine(name, dtype)
+    plain = PlainNifulix(folders[name])
+    vocab = CONFIGS[name]["vocab"]
+    prompts = [random_tokens(50, 9, vocab), random_tokens(51, 70, vocab), random_tokens(52, 1, vocab)]
+    outs = e.generate(prompts, max_tokens=12, temperature=0.0, stop_token_ids=[])
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        ref = plain.forward(list(p) + o)
+        for j, tok in enumerate(o):                        # the chosen token is the oracle's, or ties with it to rounding
+            row = ref[len(p) - 1 + j]
+            assert row.max() - row[tok] <= 2 * TOL[dtype] * np.abs(row).max(), (j, tok, int(row.argmax()))
+    if dtype == "float32":
+        assert outs == [plain.greedy(p, 12) for p in prompts]
+    # batches of two, one after the other, give the same tokens
+    assert e.generate(prompts, max_tokens=12, temperature=0.0, stop_token_ids=[], batch_size=2) == outs or dtype != "float32"
+    e.cache.book.check_all_free()
+
+
+def test_long_decoding_keeps_the_state_and_the_windows(engine, oracle):
+    e = engine("P", "float32")
+    toks = random_tokens(61, 700, CONFIGS["P"]["vocab"])
+    ref = oracle("P", toks)
+    s = e.open()
+    e.step([StepEntry(s, toks[:5], [])])
+    for p in range(5, 700):
+        got = e.step([StepEntry(s, [toks[p]], [0])])
+        if p % 50 == 0 or p > 690:
+            close(got.cpu().numpy()[0], ref[p], "float32", p)
+    e.close(s)
+    e.cache.book.check_all_free()
+
+
+def test_replay_runs_the_design_as_a_subprocess(folders, oracle, tmp_path):
+    """bin/trace_run on a Nifulix folder: a batch of unequal prompts, then single tokens, one request ending early."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    vocab = CONFIGS["Q"]["vocab"]
+    a, b = random_tokens(71, 100, vocab), random_tokens(72, 30, vocab)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:90], "want": [0, 89]}, {"id": "b", "tokens": b[:25], "want": [24]}], "end": []}]
+    for j in range(10):
+        ents = [{"id": "a", "tokens": [a[90 + j]], "want": [0]}]
+        if j < 5:
+            ents.append({"id": "b", "tokens": [b[25 + j]], "want": [0]})
+        steps.append({"step": j + 1, "entries": ents, "end": (["b"] if j == 4 else []) + (["a"] if j == 9 else [])})
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders["Q"], "--dtype", "float32", "--out", str(out),
+                           "--max-tokens", "130"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(11)]
+    ra, rb = oracle("Q", a), oracle("Q", b)
+    first = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, vocab)
+    assert rel_err(first, np.stack([ra[0], ra[89], rb[24]])) < TOL["float32"]
+    for j in range(10):
+        got = np.fromfile(out / f"{j + 1}.f32", dtype="<f4").reshape(-1, vocab)
+        assert rel_err(got[0], ra[90 + j]) < TOL["float32"]
+        if j < 5:
+            assert rel_err(got[1], rb[25 + j]) < TOL["float32"]
