@@ -243,6 +243,77 @@ def self_check(engine, ref, cfg, seed):
     return float((rows[0] - rows[1]).abs().max() / rows[1].abs().max())
 
 
+def nifulix_config(width, ff, vocab, heads, dim, window):
+    """Layers that resemble a real model's: two of each kind of mixer, a gated feed-forward in every layer."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                                          "v_mix": True, "mask": {"size": window, "keep_first": 4}}}
+    ret = {"type": "retention", "mixer": {"heads": width // 128, "dim": 128, "vdim": 128, "rot": {"dims": 128, "base": 1e6},
+                                          "decay": [1.0 - 2.0 ** (-5 - i % 6) for i in range(width // 128)]}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": 3 * width // 8, "kv_rank": width // 4,
+                                                 "scale": (1.5 * dim) ** -0.5, "rot": {"base": 5e4, "dims": dim // 2}, "mask": {"size": window}}}
+    layers = [dict(l, mlp={"kind": "dense", "ff": ff}) for l in (att, ret, lat, att, ret, lat)]
+    return {"architecture": "Nifulix", "vocab": vocab, "width": width, "residual_mult": 0.3, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def design_points(args, pk, pk_src):
+    """`--design nifulix`: prefill and decode throughput of Nifulix at layer sizes that resemble a real model's, beside GPT-2 (the
+    closest model this library runs) at the same width, depth, head size and weight count of the feed-forward; and, from
+    a kernel-by-kernel pass with CUDA events around every operation, each design's mean time per operation."""
+    import torch
+    from kvad_b200 import StepEntry, profile, write_random_model
+
+    sizes = {"w1024": dict(width=1024, heads=16, dim=64, ff=2816, inner=4096), "w2048": dict(width=2048, heads=16, dim=128, ff=5632, inner=8192)}
+    vocab, ctx, window, plen = 32000, 2048, 512, 512
+    out = {"design": "nifulix", "beside": "gpt2", "dtype": args.dtype, "data": "synthetic: seeded uniform-random token ids, seeded random weights",
+           "prefill": "one step of 2 x 1024 prompt tokens, L2 flushed between iterations", "decode": f"batch {args.batch}, {plen}-token prompts, {min(args.steps, 128)} steps after {max(3, args.warmup)} warm-up steps, tokens fed back on the device",
+           "window": window, "sizes": {}}
+    for name, z in sizes.items():
+        row = {}
+        for design in ("nifulix", "gpt2"):
+            cfg = (nifulix_config(z["width"], z["ff"], vocab, z["heads"], z["dim"], window) if design == "nifulix" else
+                   dict(model_type="gpt2", n_layer=6, n_embd=z["width"], n_head=z["heads"], n_inner=z["inner"], vocab_size=vocab, n_positions=ctx,
+                        layer_norm_epsilon=1e-5, activation_function="gelu_new"))
+            with tempfile.TemporaryDirectory(prefix="kvad_b200-bench-") as d:
+                write_random_model(d, cfg, seed=0)
+                engine = build_engine(d, cfg, args.dtype, max(args.batch, 2) * ctx)
+            print(f"[bench] {name} {design}: {engine.describe()}", file=sys.stderr)
+            times = prefill_point(engine, 2, 1024, iters=5, warmup=3, seed=3)
+            pt = decode_point(engine, args.batch, plen, min(args.steps, 128), max(3, args.warmup), seed=1, rounds=max(3, args.rounds - 2))
+            r = {"params_m": round(engine.model.param_count() / 1e6, 1), "prefill_ms": round(statistics.median(times), 4),
+                 "prefill_tok_s": round(2048 / (statistics.median(times) * 1e-3), 1), "decode_tok_s": round(pt["tok_s"], 1),
+                 "decode_ms_per_step": round(pt["ms_per_step"], 5), "decode_launches_per_step": int(pt["launches"] / min(args.steps, 128)),
+                 "decode_hbm_frac": round(hbm_frac(engine, args.batch, pt, pk), 4)}
+            # kernel by kernel: one prefill step and eight decode steps with events around every operation
+            engine.use_graphs = False
+            profile.instrument(engine.ops)
+            prompts = random_prompts(2, 1024, vocab, 4)
+            for rep in range(3):
+                if rep == 2:
+                    profile.table()                     # (drops what the warm passes recorded)
+                    profile.clear()
+                slots = [engine.open() for _ in prompts]
+                engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
+                for s in slots:
+                    engine.close(s)
+            pr8 = random_prompts(args.batch, plen, vocab, 5)
+            slots = [engine.open() for _ in pr8]
+            engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, pr8)])
+            engine.decode_run(slots, [1] * len(slots), 4)
+            profile.clear(keep_rows=2048)
+            engine.decode_run(slots, [1] * len(slots), 8)
+            for s in slots:
+                engine.close(s)
+            r["op_mean_us"] = {label: round(us / n, 2) for label, n, us in profile.table()}
+            profile.clear()
+            row[design] = r
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    out["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "of": pk_src}
+    print(json.dumps(out))
+    return 0
+
+
 def build_engine(model_dir, cfg, dtype, max_tokens, no_graphs=False):
     from kvad_b200 import Engine
     engine = Engine.from_pretrained(model_dir, dtype, max_tokens=max_tokens)
@@ -304,6 +375,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="the same as --points none")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "sampled"],
                     help="`sampled`: the timed decode steps draw with temperature 0.7, top-k 40, top-p 0.95")
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix"],
+                    help="`nifulix`: instead of the headline, Nifulix beside GPT-2 at equal sizes (prefill, decode, time per operation)")
     args = ap.parse_args()
     if args.skip_points:
         args.points = "none"
@@ -329,6 +402,8 @@ def main():
     from kvad_b200 import write_random_model
 
     pk, pk_src = peaks()
+    if args.design == "nifulix":
+        return design_points(args, pk, pk_src)
     tmp = tempfile.TemporaryDirectory(prefix="kvad_b200-bench-")
     model_dir = tmp.name
     write_random_model(model_dir, cfg, seed=0)

@@ -41,7 +41,55 @@ struct ScoredArgs {
   int n_heads, n_kv_heads, dk, dv, hp, v_alias;
   float scale, softcap, slope_span;
   int window, keep_first;
+  int vec_k, vec_v;      // keys / values can be fetched in 16-byte pieces
+  int n_splits;          // > 1: the tiles of keys a block would walk are dealt out to n_splits blocks; each leaves its
+  float* partial;        // running maximum, sum and unnormalised output in `partial` [rows, heads, n_splits, dv + 2]
 };
+
+__device__ __forceinline__ void unpack16(const uint4& raw, float* f, float) {
+  f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& raw, float* f, __nv_bfloat16) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 v = __bfloat1622float2(h[t]);
+    f[2 * t] = v.x;
+    f[2 * t + 1] = v.y;
+  }
+}
+
+// `n_rows` rows of `cols` entries (row stride ld_src) into 32-bit shared memory (row stride ld_dst, `cols_to` >= cols
+// entries written, the rest zeros); rows from `n_live` on are zeros (places of the cache that no row sees yet may hold
+// anything).  `vec`: 16-byte pieces (cols, ld_src multiples of a piece, src aligned) - few, wide, independent loads.
+template <typename T>
+__device__ __forceinline__ void load_tile(float* dst, int ld_dst, const T* src, int64_t ld_src, int n_rows, int cols, int cols_to,
+                                          int n_live, bool vec, int tid) {
+  constexpr int E = 16 / (int)sizeof(T);
+  if (vec) {
+    const int cpr = cols / E;
+#pragma unroll 4
+    for (int i = tid; i < n_rows * cpr; i += THREADS) {
+      const int r = i / cpr, c = (i - r * cpr) * E;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (r < n_live) raw = *reinterpret_cast<const uint4*>(src + (int64_t)r * ld_src + c);
+      float f[E];
+      unpack16(raw, f, T());
+#pragma unroll
+      for (int e = 0; e < E; ++e) dst[r * ld_dst + c + e] = f[e];
+    }
+    for (int i = tid; i < n_rows * (cols_to - cols); i += THREADS) {
+      const int r = i / (cols_to - cols), c = cols + (i - r * (cols_to - cols));
+      dst[r * ld_dst + c] = 0.f;
+    }
+  } else {
+#pragma unroll 4
+    for (int i = tid; i < n_rows * cols_to; i += THREADS) {
+      const int r = i / cols_to, c = i - r * cols_to;
+      dst[r * ld_dst + c] = (r < n_live && c < cols) ? to_f32(src[(int64_t)r * ld_src + c]) : 0.f;
+    }
+  }
+}
 
 template <typename T, int KPL, int DPL>
 __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredArgs a) {
@@ -57,7 +105,8 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
   const int hp = a.hp, tok = TR / hp;
   const int group = a.n_heads / a.n_kv_heads, chunks = (group + hp - 1) / hp;
   const int s = blockIdx.y, kvh = blockIdx.z / chunks, chunk = blockIdx.z % chunks;
-  const int start = a.seq_starts[s], n_new = a.seq_starts[s + 1] - start, tok0 = blockIdx.x * tok;
+  const int n_splits = a.n_splits, split = blockIdx.x % n_splits;
+  const int start = a.seq_starts[s], n_new = a.seq_starts[s + 1] - start, tok0 = (blockIdx.x / n_splits) * tok;
   if (tok0 >= n_new) return;
   const int n_tok = n_new - tok0 < tok ? n_new - tok0 : tok;
   const int h0 = kvh * group + chunk * hp, n_h = group - chunk * hp < hp ? group - chunk * hp : hp;
@@ -72,12 +121,13 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
   }
   // what each of the warp's pairs is: its position, whether it exists, its head's slope
   int row_pos[RPW];
-  bool row_live[RPW];
+  bool row_live[RPW], warp_live = false;
   float row_slope[RPW];
 #pragma unroll
   for (int r = 0; r < RPW; ++r) {
     const int row = warp * RPW + r, ti = row / hp, hi = row - ti * hp;
     row_live[r] = ti < n_tok && hi < n_h;
+    warp_live = warp_live || row_live[r];
     row_pos[r] = pos0 + ti;
     row_slope[r] = a.slope_span > 0.f ? exp2f(-a.slope_span * (float)(h0 + hi + 1) / (float)a.n_heads) : 0.f;
   }
@@ -92,24 +142,22 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
   const int first_key = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;   // of the block's first token
   const T* kp = (const T*)a.k_pages;
   const T* vp = (const T*)a.v_pages;
+  int dealt = 0;
   for (int t = 0; t <= last_pos / TK; ++t) {
     const int key0 = t * TK;
     if (key0 + TK <= first_key && key0 >= a.keep_first) continue;       // (the same for every thread of the block)
+    if (dealt++ % n_splits != split) continue;
     __syncthreads();                                                    // the tile before has been used up (and Qs is written)
     const int page = pages[key0 / PAGE], in_page = key0 % PAGE;
     const T* kt = kp + (int64_t)page * a.k_page_stride + (int64_t)kvh * a.k_head_stride + (int64_t)in_page * a.ld_k;
-    for (int i = tid; i < TK * dkp; i += THREADS) {
-      const int k = i / dkp, d = i - k * dkp;
-      Ks[k * ldks + d] = (key0 + k <= last_pos && d < dk) ? to_f32(kt[(int64_t)k * a.ld_k + d]) : 0.f;   // (a place no row sees yet may hold anything)
-    }
+    const int n_live = last_pos - key0 + 1;                             // keys of the tile that exist
+    load_tile<T>(Ks, ldks, kt, a.ld_k, TK, dk, dkp, n_live, a.vec_k != 0, tid);
     if (!a.v_alias) {
       const T* vt = vp + (int64_t)page * a.v_page_stride + (int64_t)kvh * a.v_head_stride + (int64_t)in_page * a.ld_v;
-      for (int i = tid; i < TK * dv; i += THREADS) {
-        const int k = i / dv, d = i - k * dv;
-        Vs[i] = key0 + k <= last_pos ? to_f32(vt[(int64_t)k * a.ld_v + d]) : 0.f;
-      }
+      load_tile<T>(Vs, dv, vt, a.ld_v, TK, dv, dv, n_live, a.vec_v != 0, tid);
     }
     __syncthreads();
+    if (!warp_live) continue;                                           // (a warp without pairs only helps to load)
     float sc[RPW][KPL];
 #pragma unroll
     for (int r = 0; r < RPW; ++r)
@@ -183,6 +231,22 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
   }
   T* out = (T*)a.out;
   const T* gate = (const T*)a.gate;
+  if (n_splits > 1) {
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      if (!row_live[r]) continue;
+      const int row = warp * RPW + r, ti = row / hp, hi = row - ti * hp;
+      float* dst = a.partial + (((int64_t)(start + tok0 + ti) * a.n_heads + h0 + hi) * n_splits + split) * (dv + 2);
+      if (lane == 0) {
+        dst[0] = run_max[r];
+        dst[1] = run_sum[r];
+      }
+#pragma unroll
+      for (int i = 0; i < DPL; ++i)
+        if (lane + 32 * i < dv) dst[2 + lane + 32 * i] = acc[r][i];
+    }
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < RPW; ++r) {
     if (!row_live[r]) continue;
@@ -201,6 +265,35 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
   }
 }
 
+// The parts that `n_splits` blocks left of one (row, head) become its output: a block per (row, head), a thread per
+// output entry; the parts are taken in split order, so the result does not depend on which block finished first.
+template <typename T>
+__global__ void scored_merge_kernel(const float* __restrict__ partial, int n_splits, int n_heads, int dv, T* __restrict__ out,
+                                    int64_t ld_out, const T* __restrict__ gate, int64_t ld_gate) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, h = blockIdx.y;
+  const float* src = partial + ((int64_t)row * n_heads + h) * n_splits * (dv + 2);
+  float m = -INFINITY;
+#pragma unroll 4
+  for (int i = 0; i < n_splits; ++i) m = fmaxf(m, src[i * (dv + 2)]);
+  float total = 0.f;
+  for (int i = 0; i < n_splits; ++i) {
+    const float mi = src[i * (dv + 2)];
+    if (mi != -INFINITY) total = fmaf(src[i * (dv + 2) + 1], expf(mi - m), total);
+  }
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float y = 0.f;
+    for (int i = 0; i < n_splits; ++i) {
+      const float mi = src[i * (dv + 2)];
+      if (mi != -INFINITY) y = fmaf(src[i * (dv + 2) + 2 + d], expf(mi - m), y);
+    }
+    y /= total;
+    if (gate != nullptr) y *= 1.0f / (1.0f + expf(-to_f32(gate[(int64_t)row * ld_gate + (int64_t)h * dv + d])));
+    out[(int64_t)row * ld_out + (int64_t)h * dv + d] = from_f32<T>(y);
+  }
+}
+
 template <typename T, int KPL, int DPL>
 int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cudaStream_t stream) {
   static size_t configured = 0;
@@ -210,9 +303,14 @@ int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cud
     configured = smem;
   }
   const int tok = TR / a.hp, group = a.n_heads / a.n_kv_heads, chunks = (group + a.hp - 1) / a.hp;
-  dim3 grid((max_new + tok - 1) / tok, n_seqs, a.n_kv_heads * chunks);
+  dim3 grid(((max_new + tok - 1) / tok) * a.n_splits, n_seqs, a.n_kv_heads * chunks);
   kvad_launch(scored_attention_kernel<T, KPL, DPL>, grid, dim3(THREADS), smem, stream, a);
   KVAD_CHECK_LAUNCH("attention_scored");
+  if (a.n_splits > 1) {       // (rows are single tokens here: row = sequence)
+    kvad_launch(scored_merge_kernel<T>, dim3(n_seqs, a.n_heads), dim3(a.dv <= 64 ? 64 : 128), 0, stream, (const float*)a.partial, a.n_splits,
+                a.n_heads, a.dv, (T*)a.out, a.ld_out, (const T*)a.gate, a.ld_gate);
+    KVAD_CHECK_LAUNCH("attention_scored (merge)");
+  }
   return KVAD_OK;
 }
 
@@ -308,21 +406,96 @@ latent_store_kernel(const T* __restrict__ src, int64_t ld, const void* __restric
   }
 }
 
+// Head-wise linear maps for a few rows: out[r, h, :] = W_h . a[r, h, :] with W [heads, n_out, n_in] - a latent
+// road's queries carried into the latent's space, and its attended latents carried to values.  A block takes one
+// head and 32 outputs and stages up to 8 rows' inputs of that head in shared memory (32-bit); a warp has 8 of the
+// outputs and walks the inputs once for all of them, lanes striding (eight weight rows' loads in flight, each weight
+// read once for all rows); the sums meet by shuffles.
+template <typename T>
+__global__ void __launch_bounds__(128)
+linear_heads_kernel(const T* __restrict__ a, int64_t ld_a, int head_stride_a, const T* __restrict__ w, T* __restrict__ out,
+                    int64_t ld_out, int head_stride_out, int n_rows, int n_in, int n_out) {
+  constexpr int MR = 8, OPW = 8;
+  extern __shared__ float rows_in[];                  // [MR][n_in]
+  pdl_launch_dependents();
+  const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, o0 = blockIdx.y * 32 + warp * OPW;
+  const T* wh = w + (int64_t)h * n_out * n_in;
+  pdl_wait();
+  for (int r0 = 0; r0 < n_rows; r0 += MR) {
+    const int nr = n_rows - r0 < MR ? n_rows - r0 : MR;
+    __syncthreads();
+#pragma unroll 4
+    for (int i = threadIdx.x; i < MR * n_in; i += blockDim.x) {
+      const int r = i / n_in, c = i - r * n_in;
+      rows_in[i] = r < nr ? to_f32(a[(int64_t)(r0 + r) * ld_a + (int64_t)h * head_stride_a + c]) : 0.f;
+    }
+    __syncthreads();
+    float acc[OPW][MR];
+#pragma unroll
+    for (int o = 0; o < OPW; ++o)
+#pragma unroll
+      for (int r = 0; r < MR; ++r) acc[o][r] = 0.f;
+    for (int c = lane; c < n_in; c += 32) {
+      float wv[OPW];
+#pragma unroll
+      for (int o = 0; o < OPW; ++o) wv[o] = o0 + o < n_out ? to_f32(wh[(int64_t)(o0 + o) * n_in + c]) : 0.f;
+#pragma unroll
+      for (int r = 0; r < MR; ++r) {
+        const float x = rows_in[r * n_in + c];
+#pragma unroll
+        for (int o = 0; o < OPW; ++o) acc[o][r] = fmaf(wv[o], x, acc[o][r]);
+      }
+    }
+#pragma unroll
+    for (int o = 0; o < OPW; ++o)
+#pragma unroll
+      for (int r = 0; r < MR; ++r) {
+        const float v = warp_sum(acc[o][r]);
+        if (lane == 0 && r < nr && o0 + o < n_out) out[(int64_t)(r0 + r) * ld_out + (int64_t)h * head_stride_out + o0 + o] = from_f32<T>(v);
+      }
+  }
+}
+
 }  // namespace
 
+KVAD_EXPORT int kvad_linear_heads(int dtype, const void* a, int64_t ld_a, int head_stride_a, const void* w, void* out, int64_t ld_out,
+                                  int head_stride_out, int n_rows, int n_heads, int n_in, int n_out, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_in > 0 && n_out > 0, "linear_heads: bad sizes rows=%d heads=%d in=%d out=%d", n_rows, n_heads, n_in, n_out);
+  KVAD_REQUIRE(n_heads <= 65535 * 32 && (n_out + 31) / 32 <= 65535, "linear_heads: %d heads x %d outputs are more than one launch takes", n_heads, n_out);
+  const size_t smem = (size_t)8 * n_in * sizeof(float);
+  if (smem > 48 * 1024) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_heads: inputs of %d entries a head are above this kernel's limit of 1536", n_in);
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(n_heads, (n_out + 31) / 32), block(128);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(linear_heads_kernel<float>, grid, block, smem, stream, (const float*)a, ld_a, head_stride_a, (const float*)w, (float*)out, ld_out,
+                head_stride_out, n_rows, n_in, n_out);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(linear_heads_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)a, ld_a, head_stride_a, (const __nv_bfloat16*)w,
+                (__nv_bfloat16*)out, ld_out, head_stride_out, n_rows, n_in, n_out);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_heads: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("linear_heads");
+  return KVAD_OK;
+}
+
 // Rows of sequences packed one after another (`seq_starts`), each sequence's rows being its last positions
-// (`kv_lens`: its length after the step).  `hp`: heads of a key/value group a block takes together (32 / hp
+// (`kv_lens`: its length after the step).  `n_splits` > 1 (single-token rows only): the keys of a (row, head) are
+// dealt out tile by tile to that many blocks, and a second kernel merges what they leave in `partial`
+// (float32, rows x heads x n_splits x (dv + 2)).  `hp`: heads of a key/value group a block takes together (32 / hp
 // tokens a block).  `v_pages` == `k_pages` and ld_v == ld_k: values are the keys' first dv entries.
 KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, void* out, int64_t ld_out, const void* gate,
                                       int64_t ld_gate, const int* seq_starts, const int* kv_lens, const int* page_table,
                                       int table_width, const void* k_pages, const void* v_pages, int n_seqs, int n_heads,
                                       int n_kv_heads, int dk, int dv, int page_size, int max_new, int hp, float scale,
-                                      float softcap, float slope_span, int window, int keep_first, cudaStream_t stream) {
+                                      float softcap, float slope_span, int window, int keep_first, int n_splits, float* partial,
+                                      cudaStream_t stream) {
   KVAD_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && table_width > 0 && max_new >= 0,
                "attention (scored): bad sizes seqs=%d heads=%d kv_heads=%d dk=%d dv=%d", n_seqs, n_heads, n_kv_heads, dk, dv);
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention (scored): %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
   KVAD_REQUIRE(hp >= 1 && hp <= TR, "attention (scored): %d heads a block (1..%d)", hp, TR);
   KVAD_REQUIRE(keep_first >= 0, "attention (scored): keep_first %d", keep_first);
+  KVAD_REQUIRE(n_splits >= 1 && (n_splits == 1 || (max_new == 1 && partial != nullptr)),
+               "attention (scored): keys are split over blocks for single-token rows only, and need room for the parts");
   if (page_size != PAGE)
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): takes pages of %d positions, not %d", PAGE, page_size);
   KVAD_REQUIRE(n_seqs <= 65535 && n_heads <= 65535, "attention (scored): %d sequences x %d heads are more than one launch takes", n_seqs, n_heads);
@@ -336,6 +509,10 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
   a.ld_k = dk; a.k_head_stride = (int64_t)PAGE * dk; a.k_page_stride = (int64_t)n_kv_heads * PAGE * dk;
   a.ld_v = alias ? dk : dv; a.v_head_stride = (int64_t)PAGE * a.ld_v; a.v_page_stride = (int64_t)n_kv_heads * PAGE * a.ld_v;
   a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.dk = dk; a.dv = dv; a.hp = hp; a.v_alias = alias ? 1 : 0;
+  a.n_splits = n_splits; a.partial = partial;
+  const int piece = dtype == KVAD_DTYPE_F32 ? 4 : 8;
+  a.vec_k = (dk % piece == 0 && (reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) ? 1 : 0;
+  a.vec_v = (!alias && dv % piece == 0 && (reinterpret_cast<uintptr_t>(v_pages) & 15) == 0) ? 1 : 0;
   a.scale = scale; a.softcap = softcap; a.slope_span = slope_span; a.window = window; a.keep_first = window > 0 ? keep_first : 0;
   if (dtype == KVAD_DTYPE_F32) return dispatch_scored<float>(a, n_seqs, max_new, stream);
   if (dtype == KVAD_DTYPE_BF16) return dispatch_scored<__nv_bfloat16>(a, n_seqs, max_new, stream);

@@ -18,26 +18,30 @@ namespace {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// A warp per row, four rows a block.  Two passes over the row (the second finds it in the L1): the sums
-// run lane by lane in column order, then a shuffle tree - a row's bits do not depend on its company.
+// A block of 128 threads per row.  Two passes over the row (the second finds it in the L1), four entries a thread
+// and trip where the row allows 16-byte loads of 32-bit values: few trips, their loads in flight together.  The
+// sums run thread by thread in column order, then a shuffle tree and the warps in order - a row's bits do not
+// depend on its company.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(128)
 rmsnorm_kernel(const TI* __restrict__ x, int64_t ld_in, const int* __restrict__ row_index, const void* __restrict__ w,
                int w_f32, int unit_offset, TO* __restrict__ out, int64_t ld_out, int n_rows, int width, float eps) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= n_rows) return;
+  const int r = blockIdx.x;
   const TI* xr = x + (int64_t)(row_index ? row_index[r] : r) * ld_in;
   float sq = 0.f;
-  for (int c = lane; c < width; c += 32) {
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
     const float v = to_f32(xr[c]);
     sq = fmaf(v, v, sq);
   }
-  sq = warp_sum(sq);
+  sq = block_sum(sq, scratch);
   const float inv = 1.0f / sqrtf(sq / (float)width + eps);
   TO* o = out + (int64_t)r * ld_out;
-  for (int c = lane; c < width; c += 32) {
+#pragma unroll 4
+  for (int c = threadIdx.x; c < width; c += 128) {
     float g = 1.f;
     if (w != nullptr) g = load_param(w, c, w_f32) + (unit_offset ? 1.f : 0.f);
     o[c] = from_f32<TO>(to_f32(xr[c]) * inv * g);
@@ -46,36 +50,57 @@ rmsnorm_kernel(const TI* __restrict__ x, int64_t ld_in, const int* __restrict__ 
 
 // The same on the 32-bit residual stream with a pending scaled sum: v = x + mult * delta.  With `write_back`
 // (all rows are walked) v replaces x and delta is cleared for the sublayers of the next block; with a row
-// list (the head reads a few rows) nothing is written back.
+// list (the head reads a few rows) nothing is written back.  `vec`: the width is a multiple of 4 and the rows
+// start on 16-byte boundaries.
 template <typename TO>
 __global__ void __launch_bounds__(128)
 residual_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ delta, float mult, int write_back,
                         const int* __restrict__ row_index, const void* __restrict__ w, int w_f32, int unit_offset,
-                        TO* __restrict__ out, int64_t ld_out, int n_rows, int width, float eps) {
+                        TO* __restrict__ out, int64_t ld_out, int n_rows, int width, float eps, int vec) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= n_rows) return;
+  const int r = blockIdx.x;
   const int64_t src = (int64_t)(row_index ? row_index[r] : r) * width;
   float* xr = x + src;
   float* dr = delta + src;
   float sq = 0.f;
-  for (int c = lane; c < width; c += 32) {
-    const float v = fmaf(mult, dr[c], xr[c]);
-    if (write_back) {
-      xr[c] = v;
-      dr[c] = 0.f;
+  if (vec) {
+#pragma unroll 2
+    for (int c = threadIdx.x * 4; c < width; c += 512) {
+      const float4 xv = *reinterpret_cast<const float4*>(xr + c), dv = *reinterpret_cast<const float4*>(dr + c);
+      const float4 v = make_float4(fmaf(mult, dv.x, xv.x), fmaf(mult, dv.y, xv.y), fmaf(mult, dv.z, xv.z), fmaf(mult, dv.w, xv.w));
+      if (write_back) {
+        *reinterpret_cast<float4*>(xr + c) = v;
+        *reinterpret_cast<float4*>(dr + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
     }
-    sq = fmaf(v, v, sq);
+  } else {
+    for (int c = threadIdx.x; c < width; c += 128) {
+      const float v = fmaf(mult, dr[c], xr[c]);
+      if (write_back) {
+        xr[c] = v;
+        dr[c] = 0.f;
+      }
+      sq = fmaf(v, v, sq);
+    }
   }
-  sq = warp_sum(sq);
+  sq = block_sum(sq, scratch);
   const float inv = 1.0f / sqrtf(sq / (float)width + eps);
   TO* o = out + (int64_t)r * ld_out;
-  for (int c = lane; c < width; c += 32) {
-    const float v = write_back ? xr[c] : fmaf(mult, dr[c], xr[c]);     // (the lane reads what it wrote)
-    float g = 1.f;
-    if (w != nullptr) g = load_param(w, c, w_f32) + (unit_offset ? 1.f : 0.f);
-    o[c] = from_f32<TO>(v * inv * g);
+  const int step = vec ? 4 : 1;
+  for (int c0 = threadIdx.x * step; c0 < width; c0 += 128 * step) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c = c0 + e;
+      if (e < step) {
+        const float v = write_back ? xr[c] : fmaf(mult, dr[c], xr[c]);     // (the thread reads what it wrote)
+        float g = 1.f;
+        if (w != nullptr) g = load_param(w, c, w_f32) + (unit_offset ? 1.f : 0.f);
+        o[c] = from_f32<TO>(v * inv * g);
+      }
+    }
   }
 }
 
@@ -139,7 +164,7 @@ KVAD_EXPORT int kvad_rmsnorm(int in_dtype, int out_dtype, const void* x, int64_t
                              cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && width > 0 && ld_in >= width && ld_out >= width, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
   if (n_rows == 0) return KVAD_OK;
-  dim3 grid((n_rows + 3) / 4), block(128);
+  dim3 grid(n_rows), block(128);
 #define KVAD_RMS(TI, TO)                                                                                                  \
   kvad_launch(rmsnorm_kernel<TI, TO>, grid, block, 0, stream, (const TI*)x, ld_in, row_index, w, w_f32, unit_offset, (TO*)out, \
               ld_out, n_rows, width, eps)
@@ -158,13 +183,14 @@ KVAD_EXPORT int kvad_residual_rmsnorm(int out_dtype, float* x, float* delta, flo
   KVAD_REQUIRE(n_rows >= 0 && width > 0 && ld_out >= width && x != nullptr && delta != nullptr, "residual_rmsnorm: bad arguments");
   KVAD_REQUIRE(!(write_back && row_index), "residual_rmsnorm: writing back goes with walking all rows");
   if (n_rows == 0) return KVAD_OK;
-  dim3 grid((n_rows + 3) / 4), block(128);
+  dim3 grid(n_rows), block(128);
+  const int vec = (width % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0) ? 1 : 0;
   if (out_dtype == KVAD_DTYPE_F32)
     kvad_launch(residual_rmsnorm_kernel<float>, grid, block, 0, stream, x, delta, mult, write_back, row_index, w, w_f32, unit_offset,
-                (float*)out, ld_out, n_rows, width, eps);
+                (float*)out, ld_out, n_rows, width, eps, vec);
   else if (out_dtype == KVAD_DTYPE_BF16)
     kvad_launch(residual_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, x, delta, mult, write_back, row_index, w, w_f32,
-                unit_offset, (__nv_bfloat16*)out, ld_out, n_rows, width, eps);
+                unit_offset, (__nv_bfloat16*)out, ld_out, n_rows, width, eps, vec);
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "residual_rmsnorm: unknown dtype %d", out_dtype);
   KVAD_CHECK_LAUNCH("residual_rmsnorm");

@@ -94,16 +94,18 @@ _SIGNATURES = {
     "attention_scored": {
         "kvad_attention_scored": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_float, c_float, c_int, c_int, c_void_p],
+                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
         "kvad_kv_store_blend": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "kvad_linear_heads": [c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "kvad_latent_store": [c_int, c_void_p, c_int64, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                               c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "retention": {
         "kvad_retention": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
-                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                           c_float, c_float, c_int, c_void_p],
+                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_float, c_float, c_int, c_void_p],
+        "kvad_retention_needs_raw": [c_int, c_int],
     },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -720,14 +722,40 @@ class Ops:
                                    int(bool(interleaved)), _ptr(row_seq), _ptr(row_pos), _ptr(page_table), page_table.shape[1], _ptr(pages),
                                    src.shape[0], int(rank), int(rot), pages.shape[2], _stream()), h)
 
+    HEADS_LINEAR_MAX_ROWS = 64
+
+    def linear_heads(self, a, weight, out, *, head_stride_a: int, head_stride_out: int) -> None:
+        """out[r, h * head_stride_out + j] = sum_i weight[h, j, i] * a[r, h * head_stride_a + i] for every head h: one small
+        linear map per head (no bias).  Up to `HEADS_LINEAR_MAX_ROWS` rows and 768 inputs a head in ONE launch on the
+        CUDA cores (32-bit sums); more rows: one product per head through `linear` (the tensor cores where they take it)."""
+        _need_cuda(a, weight, out)
+        ld_a, ld_o = _rows_view(a, "head-wise input"), _rows_view(out, "head-wise output")
+        if weight.dim() != 3 or not weight.is_contiguous() or {a.dtype, weight.dtype, out.dtype} != {self.dtype} or out.shape[0] != a.shape[0]:
+            raise KernelError(f"linear_heads: needs [heads, out, in] weights and rows of {self.dtype}")
+        H, n_out, n_in = weight.shape
+        if (H - 1) * head_stride_a + n_in > a.shape[1] or (H - 1) * head_stride_out + n_out > out.shape[1]:
+            raise KernelError("linear_heads: the heads do not fit the rows")
+        n = a.shape[0]
+        if n <= self.HEADS_LINEAR_MAX_ROWS and n_in <= 768:
+            h = lib("attention_scored")
+            _check(h.kvad_linear_heads(self.code, _ptr(a), ld_a, int(head_stride_a), _ptr(weight), _ptr(out), ld_o, int(head_stride_out),
+                                       n, H, n_in, n_out, _stream()), h)
+            return
+        for hd in range(H):
+            self.linear(a[:, hd * head_stride_a: hd * head_stride_a + n_in], weight[hd], None,
+                        out[:, hd * head_stride_out: hd * head_stride_out + n_out])
+
     def attention_scored(self, q, out, seq_starts, kv_lens, n_seqs: int, max_new: int, page_table, k_pages, v_pages, n_heads: int,
                          scale: float, *, value_dim: Optional[int] = None, softcap: float = 0.0, slope_span: float = 0.0,
-                         window: int = 0, keep_first: int = 0, gate=None, heads_per_block: int = 1) -> None:
+                         window: int = 0, keep_first: int = 0, gate=None, heads_per_block: int = 1, n_splits: int = 1,
+                         scratch=None) -> None:
         """Softmax attention of packed rows (each sequence's rows are its last positions) over the paged cache with
         shaped scores: s = q.k * scale, capped by `softcap` * tanh(s / softcap) if positive, less slope_h * distance with
         slope_h = 2^(-slope_span (h+1) / n_heads) if `slope_span` is positive; a row sees the last `window` positions
         (0: all) and always the first `keep_first`.  `v_pages` None: the values are the first `value_dim` entries of the
-        keys.  `gate`: the output is multiplied by sigmoid(gate).  32-bit arithmetic on the CUDA cores."""
+        keys.  `gate`: the output is multiplied by sigmoid(gate).  `n_splits` > 1 (single-token rows): the keys of a
+        row and head are dealt out to that many blocks and merged by a second kernel through `scratch` (float32, rows x
+        heads x n_splits x (value size + 2)).  32-bit arithmetic on the CUDA cores."""
         _need_cuda(q, out, seq_starts, kv_lens, page_table, k_pages, v_pages, gate)
         ld_q, ld_o = _rows_view(q, "attention queries"), _rows_view(out, "attention output")
         _, n_kv, page, dk = k_pages.shape
@@ -746,18 +774,36 @@ class Ops:
             ld_g = _rows_view(gate, "attention gate")
             if gate.shape != out.shape or gate.dtype != self.dtype:
                 raise KernelError("attention_scored: the gate must have the output's shape and dtype")
+        if n_splits > 1 and (max_new != 1 or scratch is None or scratch.dtype != torch.float32
+                             or scratch.numel() < q.shape[0] * n_heads * n_splits * (dv + 2)):
+            raise KernelError("attention_scored: splitting keys goes with single-token rows and float32 scratch of rows x heads x splits x (value size + 2)")
         h = lib("attention_scored")
         _check(h.kvad_attention_scored(self.code, _ptr(q), ld_q, _ptr(out), ld_o, _ptr(gate), ld_g, _ptr(seq_starts), _ptr(kv_lens),
                                        _ptr(page_table), page_table.shape[1], _ptr(k_pages), _ptr(v_ptr), int(n_seqs), int(n_heads), n_kv,
                                        dk, dv, page, int(max_new), int(heads_per_block), float(scale), float(softcap or 0.0),
-                                       float(slope_span or 0.0), int(window or 0), int(keep_first or 0), _stream()), h)
+                                       float(slope_span or 0.0), int(window or 0), int(keep_first or 0), int(n_splits),
+                                       _ptr(scratch if n_splits > 1 else None), _stream()), h)
+        if n_splits > 1:
+            global _launches
+            _launches += 1          # the merge kernel
+
+    @staticmethod
+    def scored_splits(n_rows: int, n_kv_heads: int, group: int, reach: int, n_sms: Optional[int] = None) -> int:
+        """Into how many parts single-token rows cut the keys of a (row, key/value head): enough blocks for two
+        an SM, one part per 64 keys of `reach` (the window plus the kept first positions, or the longest sequence the
+        cache holds) at most, 16 at most.  Depends on the batch's size and the layer's constants only."""
+        blocks = max(1, n_rows * n_kv_heads * -(-group // 32))
+        want = (2 * (n_sms or sm_count())) // blocks
+        return max(1, min(want, -(-reach // 64) + 1, 16))
 
     # -- retention ------------------------------------------------------------------------
     def retention(self, q, k, v, out, state, seq_starts, kv_lens, seq_slots, n_seqs: int, decay, n_heads: int, *, inv_freq=None,
-                  rot_dims: int = 0, interleaved: bool = False, k_scale: float = 1.0, gate=None, unit_norm_eps: Optional[float] = None) -> None:
+                  rot_dims: int = 0, interleaved: bool = False, k_scale: float = 1.0, gate=None, unit_norm_eps: Optional[float] = None,
+                  raw=None) -> None:
         """Per sequence and head, over the step's rows in order: S = decay_h S + k v^T, o = S^T q, with q and k turned by
         position first (`inv_freq`, `rot_dims`), k scaled by `k_scale`; `unit_norm_eps`: o over its root mean square per
-        head; `gate`: times silu(gate).  `state` is `[slots, heads, dk, dv]` float32 and is carried on."""
+        head; `gate`: times silu(gate).  `state` is `[slots, heads, dk, dv]` float32 and is carried on.  `raw`: float32
+        scratch `[rows, heads x dv]`, needed where `retention_needs_raw` says so (a head's columns spread over blocks)."""
         _need_cuda(q, k, v, out, state, seq_starts, kv_lens, seq_slots, decay, inv_freq, gate)
         ld_q, ld_k, ld_v, ld_o = (_rows_view(t, "retention rows") for t in (q, k, v, out))
         if state.dim() != 4 or state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1] != n_heads:
@@ -776,11 +822,16 @@ class Ops:
             ld_g = _rows_view(gate, "retention gate")
             if gate.shape != out.shape or gate.dtype != self.dtype:
                 raise KernelError("retention: the gate must have the output's shape and dtype")
+        if raw is not None and (raw.dtype != torch.float32 or not raw.is_contiguous() or raw.numel() < n * n_heads * dv):
+            raise KernelError("retention: the scratch must be contiguous float32 [rows, heads x dv]")
         h = lib("retention")
-        _check(h.kvad_retention(self.code, _ptr(q), ld_q, _ptr(k), ld_k, _ptr(v), ld_v, _ptr(gate), ld_g, _ptr(out), ld_o, _ptr(state),
+        _check(h.kvad_retention(self.code, _ptr(q), ld_q, _ptr(k), ld_k, _ptr(v), ld_v, _ptr(gate), ld_g, _ptr(out), ld_o, _ptr(raw), n, _ptr(state),
                                 _ptr(seq_starts), _ptr(kv_lens), _ptr(seq_slots), _ptr(decay), _ptr(inv_freq), int(rot_dims),
                                 int(bool(interleaved)), int(n_seqs), int(n_heads), dk, dv, float(k_scale),
                                 float(unit_norm_eps or 0.0), 0 if unit_norm_eps is None else 1, _stream()), h)
+
+    def retention_needs_raw(self, dk: int, dv: int) -> bool:
+        return lib("retention").kvad_retention_needs_raw(int(dk), int(dv)) == 1
 
     # -- sampling ------------------------------------------------------------------
     ARGMAX_CHUNK = 2048

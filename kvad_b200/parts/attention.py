@@ -192,10 +192,15 @@ class ShapedScoreAttention(Mixer):
                                v_other=other, blend=self.blend if other is not None else None)
         mixed = ctx.buffer((n, self.o_width))
         group = self.n_heads // self.n_kv_heads
+        splits, scratch = 1, None
+        if b.is_decode:            # single-token rows: the keys of a row are dealt out to several blocks
+            reach = (self.window + self.keep_first) if self.window else view.page_table.shape[1] * view.page_size
+            splits = ops.scored_splits(n, self.n_kv_heads, group, reach)
+            scratch = ctx.buffer((n * self.n_heads * splits * (self.value_dim + 2),), torch.float32) if splits > 1 else None
         ops.attention_scored(q, mixed, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
                              view.v_pages, self.n_heads, self.score_scale, softcap=self.softcap, slope_span=self.slope_span,
                              window=self.window or 0, keep_first=self.keep_first, gate=gate,
-                             heads_per_block=min(group, 32) if b.is_decode else self.heads_per_block)
+                             heads_per_block=min(group, 32) if b.is_decode else self.heads_per_block, n_splits=splits, scratch=scratch)
         self.out.forward(ctx, mixed, residual, "residual")
 
 

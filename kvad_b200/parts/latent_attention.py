@@ -7,9 +7,9 @@ key/value latent and one rotated key part are cached.
 
 The cache holds [c | k_r] per position: one "head" of kv_rank + rot_dim entries and no values.  The
 keys and values of the heads are never rebuilt: q_n . (W_uk c) = (W_uk^T q_n) . c, so each head's query is
-carried into the latent's space (one small product a head), attention runs with ONE shared key [c | k_r]
-and the latent c itself as the value, and W_uv is applied to the attended latent (one small product a
-head) before the output projection.  Prompts and single-token rows take the same road.
+carried into the latent's space (a head-wise map: one launch for a few rows, one product a head for many),
+attention runs with ONE shared key [c | k_r] and the latent c itself as the value, and W_uv is applied to
+the attended latent (head-wise again) before the output projection.  Prompts and single-token rows take the same road.
 """
 from __future__ import annotations
 
@@ -47,9 +47,8 @@ class LatentAttention(Mixer):
             raise ValueError("latent attention: the rotary encoding turns exactly the rotated part")
         self.names = dict(dq_norm=dq_norm_name, dkv_norm=dkv_norm_name, uk=uk_name, uv=uv_name)
         self.q_norm = self.kv_norm = None
-        self.uk_t: list = []     # per head W_uk_h^T [kv_rank, nope_dim]
-        self.uv: list = []       # per head W_uv_h   [value_dim, kv_rank]
-        self._uk = self._uv = None
+        self._uk = None          # [heads, kv_rank, nope_dim]: head h's W_uk_h^T, the map of its query into the latent's space
+        self._uv = None          # [heads, value_dim, kv_rank]: head h's W_uv_h
 
     def children(self):
         return [self.down, self.up_q, self.out, self.position]
@@ -67,8 +66,6 @@ class LatentAttention(Mixer):
         uk = fetch(p + n["uk"]).view(self.n_heads, self.nope_dim, self.kv_rank)
         self._uk = uk.transpose(1, 2).contiguous()             # [heads, kv_rank, nope_dim]: head h's map into the latent's space
         self._uv = fetch(p + n["uv"]).view(self.n_heads, self.value_dim, self.kv_rank).contiguous()
-        self.uk_t = [self._uk[h] for h in range(self.n_heads)]
-        self.uv = [self._uv[h] for h in range(self.n_heads)]
 
     def own_tensors(self):
         return [t for t in (self.q_norm, self.kv_norm, self._uk, self._uv) if t is not None]
@@ -91,18 +88,19 @@ class LatentAttention(Mixer):
         self.up_q.forward(ctx, cq, q)
         # each head's query in the latent's space: [W_uk_h^T q_n | rotate(q_r)]
         ql = ctx.buffer((n, H * self.key_dim))
-        for hd in range(H):
-            ops.linear(q[:, hd * self.q_dim: hd * self.q_dim + self.nope_dim], self.uk_t[hd], None,
-                       ql[:, hd * self.key_dim: hd * self.key_dim + self.kv_rank])
+        ops.linear_heads(q, self._uk, ql, head_stride_a=self.q_dim, head_stride_out=self.key_dim)
         self.position.rotate_heads(ctx, q, ql, H, self.q_dim, self.nope_dim, self.key_dim, self.kv_rank)
         attended = ctx.buffer((n, H * self.kv_rank))
+        splits, scratch = 1, None
+        if b.is_decode:
+            splits = ops.scored_splits(n, 1, H, self.window or view.page_table.shape[1] * view.page_size)
+            scratch = ctx.buffer((n * H * splits * (self.kv_rank + 2),), torch.float32) if splits > 1 else None
         ops.attention_scored(ql, attended, ctx.seq_starts, ctx.kv_lens, ctx.n_seqs, b.max_new, view.page_table, view.k_pages,
                              None, H, self.score_scale, value_dim=self.kv_rank, window=self.window or 0,
-                             heads_per_block=min(H, 32) if b.is_decode else max(d for d in (1, 2, 4) if H % d == 0))
+                             heads_per_block=min(H, 32) if b.is_decode else max(d for d in (1, 2, 4) if H % d == 0),
+                             n_splits=splits, scratch=scratch)
         mixed = ctx.buffer((n, H * self.value_dim))
-        for hd in range(H):
-            ops.linear(attended[:, hd * self.kv_rank:(hd + 1) * self.kv_rank], self.uv[hd], None,
-                       mixed[:, hd * self.value_dim:(hd + 1) * self.value_dim])
+        ops.linear_heads(attended, self._uv, mixed, head_stride_a=self.kv_rank, head_stride_out=self.value_dim)
         self.out.forward(ctx, mixed, residual, "residual")
 
 

@@ -66,10 +66,11 @@ class Retention(Mixer):
         gate = buf[:, self.proj.columns(3)] if self.gated else None
         mixed = ctx.buffer((n, self.v_width))
         pos = self.position
+        raw = ctx.buffer((n, self.v_width), torch.float32) if ctx.ops.retention_needs_raw(self.key_dim, self.value_dim) else None
         ctx.ops.retention(q, k, v, mixed, ctx.state(call.cache), ctx.seq_starts, ctx.kv_lens, ctx.seq_slots, ctx.n_seqs,
                           self.decay, self.n_heads, inv_freq=pos.inv_freq if pos is not None else None,
                           rot_dims=pos.dims if pos is not None else 0, interleaved=pos.interleaved if pos is not None else False,
-                          k_scale=self.key_scale, gate=gate, unit_norm_eps=self.unit_norm_eps)
+                          k_scale=self.key_scale, gate=gate, unit_norm_eps=self.unit_norm_eps, raw=raw)
         self.out.forward(ctx, mixed, residual, "residual")
 
 

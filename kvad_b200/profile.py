@@ -23,7 +23,8 @@ import torch
 
 #: methods of `Ops` that launch kernels, and the argument whose leading size names the shape class
 _TIMED = {"embed": 4, "layernorm": 4, "linear": 3, "kv_store": 0, "attention": 0, "attention_prefill": 0, "attention_prompt": 0, "attention_decode_sums": 0,
-          "attention_decode": 0, "argmax": 0, "sample": 0}
+          "attention_decode": 0, "argmax": 0, "sample": 0,
+          "rmsnorm": 3, "scale_add": 0, "rotary": 0, "gate_mul": 2, "kv_store_blend": 0, "latent_store": 0, "attention_scored": 0, "retention": 0, "linear_heads": 0}
 
 _records: list = []       # (label, start event, end event)
 _registered = False
@@ -85,3 +86,12 @@ def report(file=None) -> None:
     for label, n, us in rows:
         print(f"{label:48s} {n:7d} {us / 1e3:10.3f} {us / n:9.2f} {100 * us / total:6.1f}%", file=file)
     _records.clear()
+
+
+def clear(keep_rows=None) -> None:
+    """Forgets what has been recorded (`keep_rows`: but for operations of that many rows)."""
+    torch.cuda.synchronize()
+    if keep_rows is None:
+        _records.clear()
+    else:
+        _records[:] = [r for r in _records if f"rows={keep_rows}" in r[0] or f" {keep_rows}x" in r[0]]

@@ -135,7 +135,8 @@ def plain_retention(q, k, v, decay, rot, k_scale, eps, gate, S0=None, pos0=0):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,dk,dv,rot", [(3, 16, 24, (8, 500.0, "half")), (2, 40, 12, (40, 1e4, "interleaved")),
-                                         (1, 64, 64, None), (2, 128, 96, (64, 1e6, "half")), (5, 4, 4, (4, 10.0, "half"))])
+                                         (1, 64, 64, None), (2, 128, 96, (64, 1e6, "half")), (5, 4, 4, (4, 10.0, "half")),
+                                         (1, 256, 40, (128, 1e4, "half")), (2, 20, 7, (10, 30.0, "interleaved"))])
 def test_retention_whole_in_portions_and_token_by_token(dtype, H, dk, dv, rot):
     rng, ops = np.random.default_rng(dk * dv), Ops(DT[dtype])
     lens = [37, 5, 70]                                     # three sequences in one launch
@@ -165,7 +166,8 @@ def test_retention_whole_in_portions_and_token_by_token(dtype, H, dk, dv, rot):
             starts = dev(np.concatenate([[0], np.cumsum(rows)]), torch.int32)
             lens_after = dev([done[s] + r for s, r in zip(live, rows)], torch.int32)
             out = torch.full((sum(rows), H * dv), float("nan"), device="cuda", dtype=DT[dtype])
-            ops.retention(q, k, v, out, state, starts, lens_after, dev([slots[s] for s in live], torch.int32), len(live), dec, H, gate=g, **kw)
+            raw = torch.full((sum(rows), H * dv), float("nan"), device="cuda") if ops.retention_needs_raw(dk, dv) else None
+            ops.retention(q, k, v, out, state, starts, lens_after, dev([slots[s] for s in live], torch.int32), len(live), dec, H, gate=g, raw=raw, **kw)
             o = out.double().cpu().numpy()
             at = 0
             for s, r in zip(live, rows):
