@@ -31,7 +31,7 @@ def _say(msg: str) -> None:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="kvad", description="kvad_b200: GPT-2 inference on one B200")
+    p = argparse.ArgumentParser(prog="kvad", description="kvad_b200: inference on one B200 for the architectures `kvad arch` lists")
     sub = p.add_subparsers(dest="command", required=True)
     run = sub.add_parser("run", help="continue a prompt")
     run.add_argument("--model", required=True, help="folder with config.json and model.safetensors")

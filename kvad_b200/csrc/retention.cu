@@ -35,10 +35,23 @@ struct RetentionArgs {
   const float* decay;                   // [heads]
   const float* inv_freq;                // [rot_dims / 2] or null
   int rot_dims, interleaved;
-  int heads, dk, dv, split, vc, fused;
+  int heads, dk, dv, split, vc, fused, vec;
   float k_scale, eps;
   int unit_norm;
 };
+
+__device__ __forceinline__ void unpack16(const uint4& raw, float* f, float) {
+  f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& raw, float* f, __nv_bfloat16) {
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 v = __bfloat1622float2(h2[t]);
+    f[2 * t] = v.x;
+    f[2 * t + 1] = v.y;
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ void finish_row(const float* o, int dv, int lane, bool unit_norm, float eps, const T* gate, T* out) {
@@ -93,21 +106,73 @@ __global__ void __launch_bounds__(256) retention_kernel(const RetentionArgs a) {
   const T* gate = (const T*)a.gate;
   T* out = (T*)a.out;
   const int half = a.inv_freq != nullptr ? a.rot_dims / 2 : 0;
+  // The rows of the batch after this one are fetched into registers, in 16-byte pieces, while this one is worked
+  // (`a.vec`: sizes, strides and addresses allow the pieces; up to NP pieces of q and of k a thread, one of v);
+  // otherwise the rows are fetched entry by entry where they are stored.
+  constexpr int E = 16 / (int)sizeof(T), NP = 4;
+  const int cpr = dkp / E, vpr = vc / E;                         // pieces of a row of q / k, of v
+  const bool ahead = a.vec != 0 && TB * cpr <= NP * nthreads && TB * vpr <= nthreads;
+  uint4 q_pf[NP], k_pf[NP], v_pf;
+  auto fetch = [&](int t0) {
+    const int nb = n_new - t0 < TB ? n_new - t0 : TB;
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      const int i = tid + u * nthreads, t = i / cpr, c = (i - t * cpr) * E;
+      q_pf[u] = k_pf[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < nb * cpr && c < dk) {
+        const int64_t row = start + t0 + t;
+        q_pf[u] = *reinterpret_cast<const uint4*>(q + row * a.ld_q + (int64_t)h * dk + c);
+        k_pf[u] = *reinterpret_cast<const uint4*>(k + row * a.ld_k + (int64_t)h * dk + c);
+      }
+    }
+    const int t = tid / vpr, c = (tid - t * vpr) * E;
+    v_pf = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < nb * vpr && v_base + c < dv) v_pf = *reinterpret_cast<const uint4*>(v + (int64_t)(start + t0 + t) * a.ld_v + (int64_t)h * dv + v_base + c);
+  };
+  if (ahead && n_new > 0) fetch(0);
   for (int t0 = 0; t0 < n_new; t0 += TB) {
     const int nb = n_new - t0 < TB ? n_new - t0 : TB;
     __syncthreads();                                            // the rows before have been used up
-    // raw rows first (plain copies, so that many loads are in flight), then the pairs are turned where they lie
+    // raw rows first, then the pairs are turned where they lie
+    if (ahead) {
+#pragma unroll
+      for (int u = 0; u < NP; ++u) {
+        const int i = tid + u * nthreads, t = i / cpr, c = (i - t * cpr) * E;
+        if (i < nb * cpr) {
+          float fq[E], fk[E];
+          unpack16(q_pf[u], fq, T());
+          unpack16(k_pf[u], fk, T());
+#pragma unroll
+          for (int e = 0; e < E; ++e) fk[e] *= (c + e < 2 * half ? 1.f : a.k_scale);      // (turned entries are scaled after turning)
+          float* qd = qs + t * lds + (c / DPT) * SEG + c % DPT;
+          float* kd = ks + t * lds + (c / DPT) * SEG + c % DPT;
+#pragma unroll
+          for (int e = 0; e < E; e += 4) {
+            *reinterpret_cast<float4*>(qd + e) = make_float4(fq[e], fq[e + 1], fq[e + 2], fq[e + 3]);
+            *reinterpret_cast<float4*>(kd + e) = make_float4(fk[e], fk[e + 1], fk[e + 2], fk[e + 3]);
+          }
+        }
+      }
+      if (tid < nb * vpr) {
+        float fv[E];
+        unpack16(v_pf, fv, T());
+#pragma unroll
+        for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(vs + tid * E + e) = make_float4(fv[e], fv[e + 1], fv[e + 2], fv[e + 3]);
+      }
+      if (t0 + TB < n_new) fetch(t0 + TB);                      // in flight while this batch is turned and walked
+    } else {
 #pragma unroll 4
-    for (int i = tid; i < nb * dkp; i += nthreads) {
-      const int t = i / dkp, d = i - t * dkp, at = t * lds + (d / DPT) * SEG + d % DPT;
-      const int64_t row = start + t0 + t;
-      qs[at] = d < dk ? to_f32(q[row * a.ld_q + (int64_t)h * dk + d]) : 0.f;
-      ks[at] = d < dk ? to_f32(k[row * a.ld_k + (int64_t)h * dk + d]) * (d < 2 * half ? 1.f : a.k_scale) : 0.f;   // (turned entries are scaled after turning)
-    }
+      for (int i = tid; i < nb * dkp; i += nthreads) {
+        const int t = i / dkp, d = i - t * dkp, at = t * lds + (d / DPT) * SEG + d % DPT;
+        const int64_t row = start + t0 + t;
+        qs[at] = d < dk ? to_f32(q[row * a.ld_q + (int64_t)h * dk + d]) : 0.f;
+        ks[at] = d < dk ? to_f32(k[row * a.ld_k + (int64_t)h * dk + d]) * (d < 2 * half ? 1.f : a.k_scale) : 0.f;
+      }
 #pragma unroll 4
-    for (int i = tid; i < nb * vc; i += nthreads) {
-      const int t = i / vc, c = i - t * vc;
-      vs[i] = v_base + c < dv ? to_f32(v[(int64_t)(start + t0 + t) * a.ld_v + (int64_t)h * dv + v_base + c]) : 0.f;
+      for (int i = tid; i < nb * vc; i += nthreads) {
+        const int t = i / vc, c = i - t * vc;
+        vs[i] = v_base + c < dv ? to_f32(v[(int64_t)(start + t0 + t) * a.ld_v + (int64_t)h * dv + v_base + c]) : 0.f;
+      }
     }
     if (half > 0) {
       __syncthreads();
@@ -126,6 +191,7 @@ __global__ void __launch_bounds__(256) retention_kernel(const RetentionArgs a) {
     }
     __syncthreads();
     if ((tid & ~31) < (vc / VPT) * split) {                     // (whole warps walk, also a thread without columns: the shuffles want them; the other warps only stage)
+#pragma unroll 4
       for (int t = 0; t < nb; ++t) {
         const float v0 = c0 < vc ? vs[t * vc + c0] : 0.f, v1 = c0 + 1 < vc ? vs[t * vc + c0 + 1] : 0.f;
         const float4* kt = reinterpret_cast<const float4*>(ks + t * lds + si * SEG);
@@ -236,6 +302,9 @@ int dispatch_retention(RetentionArgs& a, int n_seqs, int n_rows, cudaStream_t st
   const Spread z = spread_of(a.dk, a.dv);
   if (z.dpt > 32) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "retention: keys of %d entries a head are above this kernel's limit of 1024", a.dk);
   a.split = z.split; a.vc = z.vc; a.fused = z.fused;
+  const int piece = 16 / (int)sizeof(T);                        // entries of a 16-byte piece
+  a.vec = (a.dk % piece == 0 && a.dv % piece == 0 && a.vc % piece == 0 && a.ld_q % piece == 0 && a.ld_k % piece == 0 && a.ld_v % piece == 0 &&
+           ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0) ? 1 : 0;
   if (!a.fused && a.raw == nullptr) KVAD_FAIL(KVAD_ERR_ARGUMENT, "retention: heads of %d value columns need the 32-bit scratch", a.dv);
   switch (z.dpt) {
     case 8: return launch_retention<T, 8>(a, n_seqs, n_rows, stream);
@@ -262,7 +331,7 @@ KVAD_EXPORT int kvad_retention(int dtype, const void* q, int64_t ld_q, const voi
   if (n_seqs == 0) return KVAD_OK;
   RetentionArgs a;
   a.q = q; a.k = k; a.v = v; a.gate = gate; a.ld_q = ld_q; a.ld_k = ld_k; a.ld_v = ld_v; a.ld_gate = ld_gate;
-  a.out = out; a.ld_out = ld_out; a.raw = raw; a.vc = 0; a.fused = 1; a.state = state; a.seq_starts = seq_starts; a.kv_lens = kv_lens; a.seq_slots = seq_slots;
+  a.out = out; a.ld_out = ld_out; a.raw = raw; a.vc = 0; a.fused = 1; a.vec = 0; a.state = state; a.seq_starts = seq_starts; a.kv_lens = kv_lens; a.seq_slots = seq_slots;
   a.decay = decay; a.inv_freq = rot_dims > 0 ? inv_freq : nullptr; a.rot_dims = rot_dims; a.interleaved = interleaved;
   a.heads = heads; a.dk = dk; a.dv = dv; a.split = 1; a.k_scale = k_scale; a.eps = eps; a.unit_norm = unit_norm;
   if (dtype == KVAD_DTYPE_F32) return dispatch_retention<float>(a, n_seqs, n_rows, stream);

@@ -40,7 +40,7 @@ CONFIGS = {
     "P": model(48, 211, [retention(3, 16, 24, (0.9, 0.95, 0.99), rot_dims=8, base=500.0),
                          attention(4, 2, 16, 24, window=20, keep_first=3, softcap=5.0, v_mix=True),
                          latent(3, 8, 4, 12, 20, 24, window=37),
-                         attention(4, 2, 16, 24, window=9, keep_first=0, v_mix=True, scale=0.4)],
+                         attention(6, 2, 16, 24, window=9, keep_first=0, v_mix=True, scale=0.4)],
                [64, 80, None, 64], mult=0.7),
     # one key/value head, ungrouped heads, values shorter than keys, no window at all, no rotation in the retention,
     # a window that spans pages, blending that starts at the second attention layer
@@ -56,5 +56,8 @@ CONFIGS = {
                           retention(2, 64, 64, (0.98, 0.995), rot_dims=64, base=1e6),
                           attention(8, 2, 64, 64, window=64, keep_first=4, softcap=30.0, v_mix=True)],
                [256, 256, 256], mult=1.0),
+    # nothing but retention (no paged cache at all), heads whose sizes are no powers of two, one layer without a feed-forward
+    "S": model(40, 150, [retention(2, 20, 12, (0.9, 0.99), rot_dims=10, base=100.0), retention(5, 8, 8, (0.5, 0.8, 0.9, 0.95, 0.999))],
+               [None, 48], mult=0.9),
 }
-SEEDS = {"P": 5, "Q": 6, "R": 7}
+SEEDS = {"P": 5, "Q": 6, "R": 7, "S": 8}
