@@ -10,7 +10,7 @@
 // cache read by queries that were carried into the latent's space.  The output may be multiplied by
 // sigmoid(gate) where it is written.
 //
-// A block works a tile of 32 (token, head) pairs that share one key/value head - 32 / hp consecutive
+// A block works a tile of 32 (or, with eight warps, 64) (token, head) pairs that share one key/value head - 32 / hp consecutive
 // tokens of one sequence times hp heads of the group (prompts: few heads, many tokens; single-token rows:
 // one token, all heads of the group) - against the keys tile by tile: a tile of keys and values comes into
 // shared memory once for all 32 pairs.  Warp w owns pairs 8w .. 8w+7: for the scores a lane takes keys
@@ -28,7 +28,7 @@ using namespace kvad;
 
 namespace {
 
-constexpr int TR = 32, THREADS = 128, RPW = TR / (THREADS / 32), PAGE = 64;
+constexpr int RPW = 8, PAGE = 64;       // pairs a warp owns; a block of NW warps works 8 * NW pairs (4 warps: 32, 8 warps: 64)
 
 struct ScoredArgs {
   const void* q; int64_t ld_q;
@@ -64,12 +64,12 @@ __device__ __forceinline__ void unpack16(const uint4& raw, float* f, __nv_bfloat
 // anything).  `vec`: 16-byte pieces (cols, ld_src multiples of a piece, src aligned) - few, wide, independent loads.
 template <typename T>
 __device__ __forceinline__ void load_tile(float* dst, int ld_dst, const T* src, int64_t ld_src, int n_rows, int cols, int cols_to,
-                                          int n_live, bool vec, int tid) {
+                                          int n_live, bool vec, int tid, int nthreads) {
   constexpr int E = 16 / (int)sizeof(T);
   if (vec) {
     const int cpr = cols / E;
 #pragma unroll 4
-    for (int i = tid; i < n_rows * cpr; i += THREADS) {
+    for (int i = tid; i < n_rows * cpr; i += nthreads) {
       const int r = i / cpr, c = (i - r * cpr) * E;
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
       if (r < n_live) raw = *reinterpret_cast<const uint4*>(src + (int64_t)r * ld_src + c);
@@ -78,22 +78,22 @@ __device__ __forceinline__ void load_tile(float* dst, int ld_dst, const T* src, 
 #pragma unroll
       for (int e = 0; e < E; ++e) dst[r * ld_dst + c + e] = f[e];
     }
-    for (int i = tid; i < n_rows * (cols_to - cols); i += THREADS) {
+    for (int i = tid; i < n_rows * (cols_to - cols); i += nthreads) {
       const int r = i / (cols_to - cols), c = cols + (i - r * (cols_to - cols));
       dst[r * ld_dst + c] = 0.f;
     }
   } else {
 #pragma unroll 4
-    for (int i = tid; i < n_rows * cols_to; i += THREADS) {
+    for (int i = tid; i < n_rows * cols_to; i += nthreads) {
       const int r = i / cols_to, c = i - r * cols_to;
       dst[r * ld_dst + c] = (r < n_live && c < cols) ? to_f32(src[(int64_t)r * ld_src + c]) : 0.f;
     }
   }
 }
 
-template <typename T, int KPL, int DPL>
-__global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredArgs a) {
-  constexpr int TK = 32 * KPL;
+template <typename T, int KPL, int DPL, int NW>
+__global__ void __launch_bounds__(32 * NW) scored_attention_kernel(const ScoredArgs a) {
+  constexpr int TK = 32 * KPL, TR = RPW * NW, THREADS = 32 * NW;
   extern __shared__ float smem[];
   const int dk = a.dk, dv = a.dv, dkp = (dk + 3) & ~3, ldks = dkp + 1, ldvs = a.v_alias ? ldks : dv;   // (keys padded with zeros to fours)
   float* Qs = smem;                                   // [TR][dkp]
@@ -151,10 +151,10 @@ __global__ void __launch_bounds__(THREADS) scored_attention_kernel(const ScoredA
     const int page = pages[key0 / PAGE], in_page = key0 % PAGE;
     const T* kt = kp + (int64_t)page * a.k_page_stride + (int64_t)kvh * a.k_head_stride + (int64_t)in_page * a.ld_k;
     const int n_live = last_pos - key0 + 1;                             // keys of the tile that exist
-    load_tile<T>(Ks, ldks, kt, a.ld_k, TK, dk, dkp, n_live, a.vec_k != 0, tid);
+    load_tile<T>(Ks, ldks, kt, a.ld_k, TK, dk, dkp, n_live, a.vec_k != 0, tid, THREADS);
     if (!a.v_alias) {
       const T* vt = vp + (int64_t)page * a.v_page_stride + (int64_t)kvh * a.v_head_stride + (int64_t)in_page * a.ld_v;
-      load_tile<T>(Vs, dv, vt, a.ld_v, TK, dv, dv, n_live, a.vec_v != 0, tid);
+      load_tile<T>(Vs, dv, vt, a.ld_v, TK, dv, dv, n_live, a.vec_v != 0, tid, THREADS);
     }
     __syncthreads();
     if (!warp_live) continue;                                           // (a warp without pairs only helps to load)
@@ -294,17 +294,18 @@ __global__ void scored_merge_kernel(const float* __restrict__ partial, int n_spl
   }
 }
 
-template <typename T, int KPL, int DPL>
+template <typename T, int KPL, int DPL, int NW>
 int launch_scored(const ScoredArgs& a, int n_seqs, int max_new, size_t smem, cudaStream_t stream) {
+  constexpr int TR = RPW * NW, THREADS = 32 * NW;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(scored_attention_kernel<T, KPL, DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(scored_attention_kernel<T, KPL, DPL, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) KVAD_FAIL(KVAD_ERR_CUDA, "attention (scored): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = smem;
   }
   const int tok = TR / a.hp, group = a.n_heads / a.n_kv_heads, chunks = (group + a.hp - 1) / a.hp;
   dim3 grid(((max_new + tok - 1) / tok) * a.n_splits, n_seqs, a.n_kv_heads * chunks);
-  kvad_launch(scored_attention_kernel<T, KPL, DPL>, grid, dim3(THREADS), smem, stream, a);
+  kvad_launch(scored_attention_kernel<T, KPL, DPL, NW>, grid, dim3(THREADS), smem, stream, a);
   KVAD_CHECK_LAUNCH("attention_scored");
   if (a.n_splits > 1) {       // (rows are single tokens here: row = sequence)
     kvad_launch(scored_merge_kernel<T>, dim3(n_seqs, a.n_heads), dim3(a.dv <= 64 ? 64 : 128), 0, stream, (const float*)a.partial, a.n_splits,
@@ -318,24 +319,32 @@ template <typename T>
 int dispatch_scored(const ScoredArgs& a, int n_seqs, int max_new, cudaStream_t stream) {
   const size_t limit = 200 * 1024;
   const size_t dkp = (size_t)((a.dk + 3) & ~3);
-  auto need = [&](int tk) {
-    return ((size_t)TR * dkp + (size_t)tk * (dkp + 1) + (a.v_alias ? 0 : (size_t)tk * a.dv) + (size_t)TR * tk) * sizeof(float);
+  auto need = [&](int tk, int tr) {
+    return ((size_t)tr * dkp + (size_t)tk * (dkp + 1) + (a.v_alias ? 0 : (size_t)tk * a.dv) + (size_t)tr * tk) * sizeof(float);
   };
-  const int kpl = need(64) <= limit ? 2 : 1;
-  const size_t smem = need(32 * kpl);
-  if (smem > limit) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): keys of %d and values of %d entries do not fit shared memory", a.dk, a.dv);
   const int dpl = (a.dv + 31) / 32;
-#define KVAD_SC(K, D) return launch_scored<T, K, D>(a, n_seqs, max_new, smem, stream)
-#define KVAD_SC_D(K)                      \
-  do {                                    \
-    if (dpl <= 1) KVAD_SC(K, 1);          \
-    if (dpl <= 2) KVAD_SC(K, 2);          \
-    if (dpl <= 4) KVAD_SC(K, 4);          \
-    if (dpl <= 8) KVAD_SC(K, 8);          \
-    if (dpl <= 16) KVAD_SC(K, 16);        \
+  // Long values make a block heavy in registers and shared memory, so that one block an SM is all that fits: prompts
+  // then take blocks of eight warps (64 pairs against the same tile of keys) where those fit, single-token rows never.
+  const bool wide = max_new > 1 && dpl > 2 && need(64, 64) <= limit && need(64, 32) > 100 * 1024;
+  const int kpl = need(64, 32) <= limit ? 2 : 1;
+  const size_t smem = need(32 * kpl, wide ? 64 : 32);
+  if (smem > limit) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): keys of %d and values of %d entries do not fit shared memory", a.dk, a.dv);
+#define KVAD_SC(K, D, W) return launch_scored<T, K, D, W>(a, n_seqs, max_new, smem, stream)
+#define KVAD_SC_D(K, W)                      \
+  do {                                       \
+    if (dpl <= 1) KVAD_SC(K, 1, W);          \
+    if (dpl <= 2) KVAD_SC(K, 2, W);          \
+    if (dpl <= 4) KVAD_SC(K, 4, W);          \
+    if (dpl <= 8) KVAD_SC(K, 8, W);          \
+    if (dpl <= 16) KVAD_SC(K, 16, W);        \
   } while (0)
-  if (kpl == 2) KVAD_SC_D(2);
-  else KVAD_SC_D(1);
+  if (wide) {
+    if (dpl <= 4) KVAD_SC(2, 4, 8);
+    if (dpl <= 8) KVAD_SC(2, 8, 8);
+    if (dpl <= 16) KVAD_SC(2, 16, 8);
+  }
+  if (kpl == 2) KVAD_SC_D(2, 4);
+  else KVAD_SC_D(1, 4);
 #undef KVAD_SC_D
 #undef KVAD_SC
   KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): values of %d entries are above this kernel's limit of 512", a.dv);
@@ -408,17 +417,17 @@ latent_store_kernel(const T* __restrict__ src, int64_t ld, const void* __restric
 
 // Head-wise linear maps for a few rows: out[r, h, :] = W_h . a[r, h, :] with W [heads, n_out, n_in] - a latent
 // road's queries carried into the latent's space, and its attended latents carried to values.  A block takes one
-// head and 32 outputs and stages up to 8 rows' inputs of that head in shared memory (32-bit); a warp has 8 of the
-// outputs and walks the inputs once for all of them, lanes striding (eight weight rows' loads in flight, each weight
-// read once for all rows); the sums meet by shuffles.
+// head and 8 outputs (many small blocks: the maps are short chains of loads, and only blocks side by side hide
+// them) and stages up to 8 rows' inputs of that head in shared memory (32-bit); a warp has 2 of the outputs and
+// walks the inputs once for both, lanes striding, four trips' loads in flight; the sums meet by shuffles.
 template <typename T>
 __global__ void __launch_bounds__(128)
 linear_heads_kernel(const T* __restrict__ a, int64_t ld_a, int head_stride_a, const T* __restrict__ w, T* __restrict__ out,
                     int64_t ld_out, int head_stride_out, int n_rows, int n_in, int n_out) {
-  constexpr int MR = 8, OPW = 8;
+  constexpr int MR = 8, OPW = 2;
   extern __shared__ float rows_in[];                  // [MR][n_in]
   pdl_launch_dependents();
-  const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, o0 = blockIdx.y * 32 + warp * OPW;
+  const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, o0 = blockIdx.y * (4 * OPW) + warp * OPW;
   const T* wh = w + (int64_t)h * n_out * n_in;
   pdl_wait();
   for (int r0 = 0; r0 < n_rows; r0 += MR) {
@@ -435,6 +444,7 @@ linear_heads_kernel(const T* __restrict__ a, int64_t ld_a, int head_stride_a, co
     for (int o = 0; o < OPW; ++o)
 #pragma unroll
       for (int r = 0; r < MR; ++r) acc[o][r] = 0.f;
+#pragma unroll 4
     for (int c = lane; c < n_in; c += 32) {
       float wv[OPW];
 #pragma unroll
@@ -461,11 +471,11 @@ linear_heads_kernel(const T* __restrict__ a, int64_t ld_a, int head_stride_a, co
 KVAD_EXPORT int kvad_linear_heads(int dtype, const void* a, int64_t ld_a, int head_stride_a, const void* w, void* out, int64_t ld_out,
                                   int head_stride_out, int n_rows, int n_heads, int n_in, int n_out, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && n_heads > 0 && n_in > 0 && n_out > 0, "linear_heads: bad sizes rows=%d heads=%d in=%d out=%d", n_rows, n_heads, n_in, n_out);
-  KVAD_REQUIRE(n_heads <= 65535 * 32 && (n_out + 31) / 32 <= 65535, "linear_heads: %d heads x %d outputs are more than one launch takes", n_heads, n_out);
+  KVAD_REQUIRE(n_heads <= 65535 * 32 && (n_out + 7) / 8 <= 65535, "linear_heads: %d heads x %d outputs are more than one launch takes", n_heads, n_out);
   const size_t smem = (size_t)8 * n_in * sizeof(float);
   if (smem > 48 * 1024) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_heads: inputs of %d entries a head are above this kernel's limit of 1536", n_in);
   if (n_rows == 0) return KVAD_OK;
-  dim3 grid(n_heads, (n_out + 31) / 32), block(128);
+  dim3 grid(n_heads, (n_out + 7) / 8), block(128);
   if (dtype == KVAD_DTYPE_F32)
     kvad_launch(linear_heads_kernel<float>, grid, block, smem, stream, (const float*)a, ld_a, head_stride_a, (const float*)w, (float*)out, ld_out,
                 head_stride_out, n_rows, n_in, n_out);
@@ -492,7 +502,7 @@ KVAD_EXPORT int kvad_attention_scored(int dtype, const void* q, int64_t ld_q, vo
   KVAD_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && table_width > 0 && max_new >= 0,
                "attention (scored): bad sizes seqs=%d heads=%d kv_heads=%d dk=%d dv=%d", n_seqs, n_heads, n_kv_heads, dk, dv);
   KVAD_REQUIRE(n_heads % n_kv_heads == 0, "attention (scored): %d heads do not divide into %d key/value heads", n_heads, n_kv_heads);
-  KVAD_REQUIRE(hp >= 1 && hp <= TR, "attention (scored): %d heads a block (1..%d)", hp, TR);
+  KVAD_REQUIRE(hp >= 1 && hp <= 32, "attention (scored): %d heads a block (1..32)", hp);
   KVAD_REQUIRE(keep_first >= 0, "attention (scored): keep_first %d", keep_first);
   KVAD_REQUIRE(n_splits >= 1 && (n_splits == 1 || (max_new == 1 && partial != nullptr)),
                "attention (scored): keys are split over blocks for single-token rows only, and need room for the parts");
