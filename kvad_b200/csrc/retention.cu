@@ -191,33 +191,51 @@ __global__ void __launch_bounds__(256) retention_kernel(const RetentionArgs a) {
     }
     __syncthreads();
     if ((tid & ~31) < (vc / VPT) * split) {                     // (whole warps walk, also a thread without columns: the shuffles want them; the other warps only stage)
-#pragma unroll 4
-      for (int t = 0; t < nb; ++t) {
-        const float v0 = c0 < vc ? vs[t * vc + c0] : 0.f, v1 = c0 + 1 < vc ? vs[t * vc + c0 + 1] : 0.f;
-        const float4* kt = reinterpret_cast<const float4*>(ks + t * lds + si * SEG);
-        const float4* qt = reinterpret_cast<const float4*>(qs + t * lds + si * SEG);
-        float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
+      // four rows at a time: their loads and multiply-adds first (only the state links them), then the lanes' sums
+      // of all four meet by shuffles side by side, then the stores - so that no row waits for the one before it
+      for (int tb = 0; tb < nb; tb += 4) {
+        float r0[4], r1[4];
 #pragma unroll
-        for (int j4 = 0; j4 < DPT / 4; ++j4) {
-          const float4 kk = kt[j4], qq = qt[j4];
-          const float kj[4] = {kk.x, kk.y, kk.z, kk.w}, qj[4] = {qq.x, qq.y, qq.z, qq.w};
+        for (int w = 0; w < 4; ++w) {
+          const int t = tb + w;
+          r0[w] = r1[w] = 0.f;
+          if (t < nb) {                                         // (the same for the whole block)
+            const float v0 = c0 < vc ? vs[t * vc + c0] : 0.f, v1 = c0 + 1 < vc ? vs[t * vc + c0 + 1] : 0.f;
+            const float4* kt = reinterpret_cast<const float4*>(ks + t * lds + si * SEG);
+            const float4* qt = reinterpret_cast<const float4*>(qs + t * lds + si * SEG);
+            float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int j = j4 * 4 + u;
-            S0[j] = fmaf(kj[u], v0, decay * S0[j]);
-            S1[j] = fmaf(kj[u], v1, decay * S1[j]);
-            o0[u] = fmaf(S0[j], qj[u], o0[u]);
-            o1[u] = fmaf(S1[j], qj[u], o1[u]);
+            for (int j4 = 0; j4 < DPT / 4; ++j4) {
+              const float4 kk = kt[j4], qq = qt[j4];
+              const float kj[4] = {kk.x, kk.y, kk.z, kk.w}, qj[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int j = j4 * 4 + u;
+                S0[j] = fmaf(kj[u], v0, decay * S0[j]);
+                S1[j] = fmaf(kj[u], v1, decay * S1[j]);
+                o0[u] = fmaf(S0[j], qj[u], o0[u]);
+                o1[u] = fmaf(S1[j], qj[u], o1[u]);
+              }
+            }
+            r0[w] = (o0[0] + o0[1]) + (o0[2] + o0[3]);
+            r1[w] = (o1[0] + o1[1]) + (o1[2] + o1[3]);
           }
         }
-        float r0 = (o0[0] + o0[1]) + (o0[2] + o0[3]), r1 = (o1[0] + o1[1]) + (o1[2] + o1[3]);
         for (int m = 1; m < split; m <<= 1) {
-          r0 += __shfl_xor_sync(0xffffffffu, r0, m);
-          r1 += __shfl_xor_sync(0xffffffffu, r1, m);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            r0[w] += __shfl_xor_sync(0xffffffffu, r0[w], m);
+            r1[w] += __shfl_xor_sync(0xffffffffu, r1[w], m);
+          }
         }
         if (si == 0 && c0 < vc) {
-          os[t * vc + c0] = r0;
-          if (c0 + 1 < vc) os[t * vc + c0 + 1] = r1;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            if (tb + w < nb) {
+              os[(tb + w) * vc + c0] = r0[w];
+              if (c0 + 1 < vc) os[(tb + w) * vc + c0 + 1] = r1[w];
+            }
+          }
         }
       }
     }
