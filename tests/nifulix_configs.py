@@ -56,8 +56,15 @@ CONFIGS = {
                           retention(2, 64, 64, (0.98, 0.995), rot_dims=64, base=1e6),
                           attention(8, 2, 64, 64, window=64, keep_first=4, softcap=30.0, v_mix=True)],
                [256, 256, 256], mult=1.0),
+    # long keys and values (the heavy forms of the kernels: blocks of eight warps, states spread over blocks, the head-wise
+    # maps as one product a head), keys and values of different sizes, more kept first tokens than a page
+    "T": model(256, 400, [latent(4, 32, 32, 32, 96, 224, window=200, base=5e4),
+                          attention(8, 2, 128, 96, window=150, keep_first=70, softcap=25.0, v_mix=True),
+                          retention(2, 128, 128, (0.99, 0.999), rot_dims=128, base=1e6),
+                          attention(4, 2, 160, 96, v_mix=True)],
+               [320, None, 320, 320], mult=0.4),
     # nothing but retention (no paged cache at all), heads whose sizes are no powers of two, one layer without a feed-forward
     "S": model(40, 150, [retention(2, 20, 12, (0.9, 0.99), rot_dims=10, base=100.0), retention(5, 8, 8, (0.5, 0.8, 0.9, 0.95, 0.999))],
                [None, 48], mult=0.9),
 }
-SEEDS = {"P": 5, "Q": 6, "R": 7, "S": 8}
+SEEDS = {"P": 5, "Q": 6, "R": 7, "S": 8, "T": 9}

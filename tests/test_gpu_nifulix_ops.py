@@ -260,7 +260,8 @@ class Paged:
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,dk,dv,window,keep,cap,span", [
     (4, 2, 16, 24, 20, 3, 5.0, 8.0), (3, 3, 32, 16, None, 0, None, 8.0), (6, 1, 20, 40, 70, 0, 30.0, 0.0),
-    (8, 2, 64, 64, 64, 4, 30.0, 8.0), (2, 1, 6, 130, 129, 66, None, 2.0)])
+    (8, 2, 64, 64, 64, 4, 30.0, 8.0), (2, 1, 6, 130, 129, 66, None, 2.0),
+    (4, 2, 160, 160, 100, 3, 10.0, 8.0)])      # (long keys and values: prompts take blocks of eight warps)
 def test_scored_attention_prompts_portions_and_single_rows(dtype, H, G, dk, dv, window, keep, cap, span):
     rng, ops, scale = np.random.default_rng(H * dk + dv), Ops(DT[dtype]), 0.3
     lens = [150, 9, 70]
@@ -363,14 +364,16 @@ def test_values_blended_where_they_are_stored(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_latent_rows_normalised_turned_and_read_as_keys_and_values(dtype):
+@pytest.mark.parametrize("sizes", [(3, 8, 4, 12, 20, 100, 37), (4, 32, 32, 16, 256, 150, 70)])      # (the second: blocks of eight warps, 16-byte loads)
+def test_latent_rows_normalised_turned_and_read_as_keys_and_values(dtype, sizes):
     """The latent cache: a row is [norm(c) | rotate(k_r)]; queries carried into the latent's space attend over it with
     the latent as the value.  Against the plain form that rebuilds every head's keys and values from the latent."""
     rng, ops = np.random.default_rng(9), Ops(DT[dtype])
-    H, dn, dr, dv, rk, n, eps, base, window, scale = 3, 8, 4, 12, 20, 100, 1e-5, 50.0, 37, 0.3
+    H, dn, dr, dv, rk, n, window = sizes
+    eps, base, scale = 1e-5, 50.0, 0.3 * (8.0 / dn) ** 0.5
     raw = rng.standard_normal((n, rk + dr))
     w = 1 + 0.1 * rng.standard_normal(rk)
-    uk, uv = rng.standard_normal((H * dn, rk)) * 0.3, rng.standard_normal((H * dv, rk)) * 0.3
+    uk, uv = rng.standard_normal((H * dn, rk)) * 0.3 * (20.0 / rk) ** 0.5, rng.standard_normal((H * dv, rk)) * 0.3 * (20.0 / rk) ** 0.5
     q = rng.standard_normal((n, H, dn + dr))
     cache = Paged([n], 1, rk + dr, rk, dtype, seed=2, alias=True)
     seq, pos = cache.rows_meta([(0, n)])
@@ -381,6 +384,7 @@ def test_latent_rows_normalised_turned_and_read_as_keys_and_values(dtype):
     k_r = pl.rotate(rs[:, None, rk:], np.arange(n), base, dr, "interleaved")[:, 0]
     page = cache.table[0, 1]
     assert rel(cache.k_pages[page, 0, 5], np.concatenate([c[69], k_r[69]])) < KTOL[dtype]
+    heads_a_block = 1 if H == 3 else 4
     # plain: per head keys and values from the latent
     qs = stored(q, dtype)
     q_r = pl.rotate(qs[..., dn:], np.arange(n), base, dr, "interleaved")
@@ -393,6 +397,6 @@ def test_latent_rows_normalised_turned_and_read_as_keys_and_values(dtype):
     ql = np.concatenate([np.einsum("nhd,hdr->nhr", qs[..., :dn], uk.reshape(H, dn, rk)), q_r], -1).reshape(n, -1)
     out = torch.full((n, H * rk), float("nan"), device="cuda", dtype=DT[dtype])
     ops.attention_scored(dev(ql, DT[dtype]), out, dev([0, n], torch.int32), dev([n], torch.int32), 1, n, cache.table_dev, cache.k_pages, None,
-                         H, scale, value_dim=rk, window=window, heads_per_block=1)
+                         H, scale, value_dim=rk, window=window, heads_per_block=heads_a_block)
     got = np.einsum("nhr,hvr->nhv", out.double().cpu().numpy().reshape(n, H, rk), uv.reshape(H, dv, rk))
     assert rel(torch.as_tensor(got), want) < KTOL[dtype] * 3
