@@ -325,7 +325,7 @@ int dispatch_scored(const ScoredArgs& a, int n_seqs, int max_new, cudaStream_t s
   const int dpl = (a.dv + 31) / 32;
   // Long values make a block heavy in registers and shared memory, so that one block an SM is all that fits: prompts
   // then take blocks of eight warps (64 pairs against the same tile of keys) where those fit, single-token rows never.
-  const bool wide = max_new > 1 && dpl > 2 && need(64, 64) <= limit && need(64, 32) > 100 * 1024;
+  const bool wide = max_new > 1 && dpl >= 2 && need(64, 64) <= limit;
   const int kpl = need(64, 32) <= limit ? 2 : 1;
   const size_t smem = need(32 * kpl, wide ? 64 : 32);
   if (smem > limit) KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "attention (scored): keys of %d and values of %d entries do not fit shared memory", a.dk, a.dv);
@@ -339,6 +339,7 @@ int dispatch_scored(const ScoredArgs& a, int n_seqs, int max_new, cudaStream_t s
     if (dpl <= 16) KVAD_SC(K, 16, W);        \
   } while (0)
   if (wide) {
+    if (dpl <= 2) KVAD_SC(2, 2, 8);
     if (dpl <= 4) KVAD_SC(2, 4, 8);
     if (dpl <= 8) KVAD_SC(2, 8, 8);
     if (dpl <= 16) KVAD_SC(2, 16, 8);
