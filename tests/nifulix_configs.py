@@ -63,8 +63,15 @@ CONFIGS = {
                           retention(2, 128, 128, (0.99, 0.999), rot_dims=128, base=1e6),
                           attention(4, 2, 160, 96, v_mix=True)],
                [320, None, 320, 320], mult=0.4),
+    # sizes that are multiples of nothing in particular: the products' and the kernels' roads for rows and heads that allow
+    # no 16-byte pieces, groups of two heads, a window and kept tokens that end inside a page
+    "U": model(100, 333, [attention(6, 3, 20, 28, window=33, keep_first=2, softcap=12.0, v_mix=True, scale=0.3),
+                          retention(3, 12, 20, (0.9, 0.97, 0.995), rot_dims=6, base=300.0),
+                          latent(5, 12, 6, 10, 36, 50, window=45, base=700.0),
+                          attention(3, 3, 20, 28, window=70, keep_first=9, v_mix=True)],
+               [130, 130, 70, None], mult=0.6, eps=1e-4),
     # nothing but retention (no paged cache at all), heads whose sizes are no powers of two, one layer without a feed-forward
     "S": model(40, 150, [retention(2, 20, 12, (0.9, 0.99), rot_dims=10, base=100.0), retention(5, 8, 8, (0.5, 0.8, 0.9, 0.95, 0.999))],
                [None, 48], mult=0.9),
 }
-SEEDS = {"P": 5, "Q": 6, "R": 7, "S": 8, "T": 9}
+SEEDS = {"P": 5, "Q": 6, "R": 7, "S": 8, "T": 9, "U": 10}
