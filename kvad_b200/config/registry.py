@@ -29,6 +29,9 @@ class Architecture:
     write_config: Optional[Callable[[Any], dict]] = None
     #: (typed configuration, rng) -> {tensor name: (array, dtype name)} (random-weights mode)
     random_tensors: Optional[Callable[[Any, Any], dict]] = None
+    #: (typed configuration, shape_of) -> typed configuration: sizes that config.json does not name and only the
+    #: checkpoint's tensors give; `shape_of(name)` is a stored tensor's shape or None
+    with_checkpoint_shapes: Optional[Callable[[Any, Any], Any]] = None
 
 
 _REGISTRY: dict[str, Architecture] = {}

@@ -1,0 +1,251 @@
+// A routed feed-forward: every row picks `top` of E experts, each a small gated feed-forward of its own.
+//
+//   moe_route        z = router logits (32-bit) -> the `top` largest (ties: the lower index), weights = softmax over
+//                    the chosen logits only
+//   moe_sort         the (row, choice) slots grouped by expert, each expert's list padded to whole tiles of 32
+//                    positions; tile -> expert, position -> row and position -> slot (-1: padding)
+//   grouped_linear   out[position] = W[expert of the position's tile] . a[row of the position]: a tiled product on
+//                    the CUDA cores (32-bit sums in k order, so a row's bits do not depend on its tile's company),
+//                    reading its rows and writing its outputs through the position lists
+//   clamped_glu      g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(alpha g) (u + 1)
+//   moe_combine      residual[row] += sum over the row's choices, in order, of weight * expert output
+//
+// How many tiles a step can need depends only on its shape (rows x top / 32 + E at most), so the launches do not
+// depend on the routing and a step can be captured; tiles past the used ones leave at once.
+#include "common.cuh"
+
+using namespace kvad;
+
+namespace {
+
+constexpr int TM = 32, TN = 64, TK = 32;
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n_rows, int n_experts, int top,
+                                 int* __restrict__ chosen, float* __restrict__ weight) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const float* z = logits + (int64_t)r * ld;
+  int* mine = chosen + (int64_t)r * top;
+  float* wt = weight + (int64_t)r * top;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = -1;
+    for (int e = 0; e < n_experts; ++e) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken = taken || mine[j] == e;
+      const float v = z[e];
+      if (!taken && (at < 0 || v > best)) {
+        best = v;
+        at = e;
+      }
+    }
+    mine[k] = at;
+    wt[k] = best;
+  }
+  const float top_z = wt[0];
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    wt[k] = expf(wt[k] - top_z);
+    sum += wt[k];
+  }
+  for (int k = 0; k < top; ++k) wt[k] /= sum;
+}
+
+// One block.  counts -> padded offsets -> places.  Which place a slot gets inside its expert's list is not fixed
+// (shared-memory atomics); no result depends on it.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_experts, int max_tiles, int* __restrict__ tile_expert,
+                int* __restrict__ pos_row, int* __restrict__ pos_slot) {
+  extern __shared__ int sm[];
+  int* counts = sm;
+  int* offsets = sm + n_experts;
+  int* cursor = sm + 2 * n_experts;
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = cursor[e] = 0;
+  for (int i = threadIdx.x; i < max_tiles * TM; i += blockDim.x) pos_row[i] = pos_slot[i] = -1;
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) atomicAdd(&counts[chosen[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tile = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offsets[e] = tile * TM;
+      const int n = (counts[e] + TM - 1) / TM;
+      for (int t = 0; t < n; ++t) tile_expert[tile + t] = e;
+      tile += n;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+    const int e = chosen[i];
+    const int at = offsets[e] + atomicAdd(&cursor[e], 1);
+    pos_row[at] = i / top;
+    pos_slot[at] = i;
+  }
+}
+
+// Tile of 32 positions x 64 outputs, 256 threads, a thread 2 x 4 outputs; K in steps of 32 through shared memory.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+grouped_linear_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict__ in_rows, const T* __restrict__ w,
+                      int64_t expert_stride, TO* __restrict__ out, int64_t ld_out, const int* __restrict__ out_rows,
+                      const int* __restrict__ valid, const int* __restrict__ tile_expert, int n_out, int k_dim) {
+  __shared__ __align__(16) float As[TK][TM + 2];
+  __shared__ __align__(16) float Ws[TK][TN + 4];
+  __shared__ int rows_in[TM], rows_out[TM];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.y, expert = tile_expert[tile];
+  if (expert < 0) return;
+  const int n0 = blockIdx.x * TN, tid = threadIdx.x;
+  if (tid < TM) {
+    const int p = tile * TM + tid;
+    const bool used = valid[p] >= 0;
+    rows_in[tid] = used ? (in_rows ? in_rows[p] : p) : -1;
+    rows_out[tid] = used ? (out_rows ? out_rows[p] : p) : -1;
+  }
+  __syncthreads();
+  const T* we = w + (int64_t)expert * expert_stride;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < k_dim; k0 += TK) {
+    for (int i = tid; i < TM * TK; i += 256) {
+      const int m = i / TK, kk = i - m * TK, r = rows_in[m];
+      As[kk][m] = (r >= 0 && k0 + kk < k_dim) ? to_f32(a[(int64_t)r * ld_a + k0 + kk]) : 0.f;
+    }
+    for (int i = tid; i < TN * TK; i += 256) {
+      const int n = i / TK, kk = i - n * TK;
+      Ws[kk][n] = (n0 + n < n_out && k0 + kk < k_dim) ? to_f32(we[(int64_t)(n0 + n) * k_dim + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
+      const float4 b = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+      acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);
+      acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
+      acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]);
+      acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = rows_out[ty * 2 + i];
+    if (r < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < n_out) out[(int64_t)r * ld_out + n] = from_f32<TO>(acc[i][j]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gate, int64_t ld_g, const T* __restrict__ up, int64_t ld_u, T* __restrict__ out,
+                                   int64_t ld_o, int n_rows, int width, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    const float g = fminf(to_f32(gate[r * ld_g + c]), limit);
+    const float u = fminf(fmaxf(to_f32(up[r * ld_u + c]), -limit), limit);
+    out[r * ld_o + c] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+}
+
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ slots, const float* __restrict__ weight,
+                                   int n_rows, int width, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width, c = i - r * width;
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(weight[r * top + k], slots[(r * top + k) * width + c], acc);
+    residual[i] += acc;
+  }
+}
+
+inline int flat_blocks(int64_t total, int threads) {
+  const int64_t b = (total + threads - 1) / threads;
+  return (int)(b < 148 * 16 ? (b < 1 ? 1 : b) : 148 * 16);
+}
+
+}  // namespace
+
+KVAD_EXPORT int kvad_moe_tile_rows() { return TM; }
+
+KVAD_EXPORT int kvad_moe_route(const float* logits, int64_t ld, int n_rows, int n_experts, int top, int* chosen, float* weight,
+                               cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && n_experts > 0 && top > 0 && top <= n_experts && ld >= n_experts, "moe_route: bad sizes experts=%d top=%d", n_experts, top);
+  if (n_rows == 0) return KVAD_OK;
+  kvad_launch(moe_route_kernel, dim3((n_rows + 63) / 64), dim3(64), 0, stream, logits, ld, n_rows, n_experts, top, chosen, weight);
+  KVAD_CHECK_LAUNCH("moe_route");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_moe_sort(const int* chosen, int n_slots, int top, int n_experts, int max_tiles, int* tile_expert, int* pos_row,
+                              int* pos_slot, cudaStream_t stream) {
+  KVAD_REQUIRE(n_slots >= 0 && top > 0 && n_experts > 0 && n_experts <= 4096, "moe_sort: bad sizes");
+  KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / TM + n_experts, "moe_sort: %d tiles cannot hold %d slots of %d experts",
+               max_tiles, n_slots, n_experts);
+  if (n_slots == 0) return KVAD_OK;
+  kvad_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, chosen, n_slots, top, n_experts, max_tiles,
+              tile_expert, pos_row, pos_slot);
+  KVAD_CHECK_LAUNCH("moe_sort");
+  return KVAD_OK;
+}
+
+// Position p reads row in_rows[p] of `a` (null: row p) and writes row out_rows[p] of `out` (null: row p); valid[p] < 0: padding.
+KVAD_EXPORT int kvad_grouped_linear(int dtype, int out_f32, const void* a, int64_t ld_a, const int* in_rows, const void* w,
+                                    int64_t expert_stride, void* out, int64_t ld_out, const int* out_rows, const int* valid,
+                                    const int* tile_expert, int max_tiles, int n_out, int k_dim, cudaStream_t stream) {
+  KVAD_REQUIRE(max_tiles >= 0 && n_out > 0 && k_dim > 0 && a && w && out && valid && tile_expert, "grouped_linear: bad arguments");
+  if (max_tiles == 0) return KVAD_OK;
+  dim3 grid((n_out + TN - 1) / TN, max_tiles), block(256);
+#define KVAD_GL(T, TO)                                                                                                       \
+  kvad_launch(grouped_linear_kernel<T, TO>, grid, block, 0, stream, (const T*)a, ld_a, in_rows, (const T*)w, expert_stride, (TO*)out, \
+              ld_out, out_rows, valid, tile_expert, n_out, k_dim)
+  if (dtype == KVAD_DTYPE_F32) KVAD_GL(float, float);
+  else if (dtype == KVAD_DTYPE_BF16 && out_f32) KVAD_GL(__nv_bfloat16, float);
+  else if (dtype == KVAD_DTYPE_BF16) KVAD_GL(__nv_bfloat16, __nv_bfloat16);
+  else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "grouped_linear: unknown dtype %d", dtype);
+#undef KVAD_GL
+  KVAD_CHECK_LAUNCH("grouped_linear");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_clamped_glu(int dtype, const void* gate, int64_t ld_g, const void* up, int64_t ld_u, void* out, int64_t ld_o,
+                                 int n_rows, int width, float limit, float alpha, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && limit > 0.f, "clamped_glu: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  dim3 grid(flat_blocks((int64_t)n_rows * width, 256)), block(256);
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(clamped_glu_kernel<float>, grid, block, 0, stream, (const float*)gate, ld_g, (const float*)up, ld_u, (float*)out, ld_o, n_rows,
+                width, limit, alpha);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(clamped_glu_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)gate, ld_g, (const __nv_bfloat16*)up, ld_u,
+                (__nv_bfloat16*)out, ld_o, n_rows, width, limit, alpha);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "clamped_glu: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("clamped_glu");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_moe_combine(float* residual, const float* slots, const float* weight, int n_rows, int width, int top,
+                                 cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && slots && weight, "moe_combine: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  kvad_launch(moe_combine_kernel, dim3(flat_blocks((int64_t)n_rows * width, 256)), dim3(256), 0, stream, residual, slots, weight, n_rows,
+              width, top);
+  KVAD_CHECK_LAUNCH("moe_combine");
+  return KVAD_OK;
+}
+
+KVAD_DEFINE_LAST_ERROR()

@@ -169,12 +169,17 @@ class Engine:
             raise KernelError("no CUDA device: kvad_b200 has no CPU path")
         torch.cuda.set_device(torch.device(device))
         arch, config = load_config(model_dir)
-        model = Model(arch.plan(config))
-        # compile (first call only) what this model's parts launch from, and no more, before the weights take time
-        from ..csrc import build
-        build.build_all(libraries_for(tdtype, model.kernel_families()), verbose=True)
         ckpt = Checkpoint.open_dir(model_dir)
         try:
+            if arch.with_checkpoint_shapes is not None:      # sizes that only the tensors' shapes give
+                def shape_of(name):
+                    e = ckpt.entries.get(name)
+                    return None if e is None else tuple(e.shape)
+                config = arch.with_checkpoint_shapes(config, shape_of)
+            model = Model(arch.plan(config))
+            # compile (first call only) what this model's parts launch from, and no more, before the weights take time
+            from ..csrc import build
+            build.build_all(libraries_for(tdtype, model.kernel_families()), verbose=True)
             source = WeightSource(ckpt, ignored_suffixes=model.plan.ignored_suffixes)
             model.load(source, tdtype, device)
         finally:

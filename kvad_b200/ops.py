@@ -107,6 +107,26 @@ _SIGNATURES = {
                            c_int, c_float, c_float, c_int, c_void_p],
         "kvad_retention_needs_raw": [c_int, c_int],
     },
+    "gated_recurrence": {
+        "kvad_gated_recurrence": [c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                  c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_int, c_float, c_float, c_void_p],
+        "kvad_gated_recurrence_state": [c_int, c_int, c_int, c_int],
+        "kvad_short_conv": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "kvad_conv_state": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "kvad_head_norm_gate": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int,
+                                c_float, c_void_p],
+    },
+    "moe": {
+        "kvad_moe_tile_rows": [],
+        "kvad_moe_route": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "kvad_grouped_linear": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_void_p],
+        "kvad_clamped_glu": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_void_p],
+        "kvad_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "kvad_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -178,6 +198,8 @@ _FAMILY_LIBRARIES = {
     "norm_rotary": {"any": ("norm_rotary",)},
     "scored_attention": {"any": ("attention_scored",)},
     "retention": {"any": ("retention",)},
+    "gated_recurrence": {"any": ("gated_recurrence",)},
+    "moe": {"any": ("moe",)},
 }
 
 
@@ -612,8 +634,9 @@ class Ops:
         _need_cuda(x, weight, out, rows)
         n, width = out.shape
         ld_in, ld_out = _rows_view(x, "rmsnorm input"), _rows_view(out, "rmsnorm output")
-        if x.shape[1] != width or out.dtype != self.dtype or x.dtype not in (torch.float32, self.dtype):
-            raise KernelError(f"rmsnorm: input must be float32 or {self.dtype} and as wide as the {self.dtype} output")
+        if (x.shape[1] != width or x.dtype not in (torch.float32, self.dtype)
+                or not (out.dtype == self.dtype or (out.dtype == torch.float32 and x.dtype == torch.float32))):
+            raise KernelError(f"rmsnorm: input must be float32 or {self.dtype} and as wide as the output ({self.dtype}, or float32 from float32)")
         if rows is None and x.shape[0] < n:
             raise KernelError("rmsnorm: fewer input rows than output rows")
         if rows is not None and (rows.dtype != torch.int32 or rows.numel() < n):
@@ -629,10 +652,10 @@ class Ops:
             if (x.dtype != torch.float32 or not x.is_contiguous() or delta.dtype != torch.float32 or not delta.is_contiguous()
                     or delta.shape != x.shape):
                 raise KernelError("rmsnorm: a deferred sum goes with the contiguous float32 stream and a sum of its shape")
-            _check(h.kvad_residual_rmsnorm(self.code, _ptr(x), _ptr(delta), float(mult), 1 if rows is None else 0, _ptr(rows),
+            _check(h.kvad_residual_rmsnorm(_code(out.dtype), _ptr(x), _ptr(delta), float(mult), 1 if rows is None else 0, _ptr(rows),
                                            _ptr(weight), w_f32, int(unit_offset), _ptr(out), ld_out, n, width, float(eps), _stream()), h)
             return
-        _check(h.kvad_rmsnorm(_code(x.dtype), self.code, _ptr(x), ld_in, _ptr(rows), _ptr(weight), w_f32, int(unit_offset), _ptr(out),
+        _check(h.kvad_rmsnorm(_code(x.dtype), _code(out.dtype), _ptr(x), ld_in, _ptr(rows), _ptr(weight), w_f32, int(unit_offset), _ptr(out),
                               ld_out, n, width, float(eps), _stream()), h)
 
     def scale_add(self, x, delta, mult: float) -> None:
@@ -832,6 +855,170 @@ class Ops:
 
     def retention_needs_raw(self, dk: int, dv: int) -> bool:
         return lib("retention").kvad_retention_needs_raw(int(dk), int(dv)) == 1
+
+    # -- recurrences with gates that depend on the token ------------------------------------
+    RECURRENCES = {"matrix_memory": 0, "delta_rule": 1}
+
+    def recurrence_state_size(self, kind: str, n_heads: int, dk: int, dv: int) -> int:
+        """32-bit numbers of state a sequence keeps for one such layer (the matrices in the kernel's own layout, and for
+        the matrix memory its normaliser and running maximum)."""
+        return int(lib("gated_recurrence").kvad_gated_recurrence_state(self.RECURRENCES[kind], int(n_heads), int(dk), int(dv)))
+
+    def gated_recurrence(self, kind: str, q, k, v, gates, out, state, seq_starts, seq_slots, n_seqs: int, n_heads: int, n_kv_heads: int,
+                         dk: int, dv: int, *, q_scale: float = 1.0, cap: float = 0.0, beta=None, a_log=None, dt_bias=None) -> None:
+        """Per sequence and head over the step's rows in order; `state` is `[slots, floats]` (32-bit), carried on.
+        `matrix_memory`: S = exp(f + m' - m) S + exp(i - m) k v^T with the running maximum m, n likewise with k alone,
+        o = S^T q / (max(|n.q|, exp(-m)) + 1e-6); `gates` float32 [rows, 2 heads] = raw input | forget projections, capped
+        here (`cap` tanh(x / cap)), the forget gate through logsigmoid.  `delta_rule`: S = g * S per key channel,
+        u = beta (v - S^T k), S += k u^T, o = S^T q; `gates` float32 [rows, heads x dk] raw, g = exp(-exp(a_log) softplus(gates +
+        dt_bias)); `beta` float32 [rows, heads].  q and k have `n_kv_heads` heads that the heads share in groups; `out` is
+        float32 [rows, heads x dv], the raw read-out."""
+        _need_cuda(q, k, v, gates, out, state, seq_starts, seq_slots, beta, a_log, dt_bias)
+        mode = self.RECURRENCES[kind]
+        ld_q, ld_k, ld_v, ld_g, ld_o = (_rows_view(t, "recurrence rows") for t in (q, k, v, gates, out))
+        n = q.shape[0]
+        if (q.shape[1] != n_kv_heads * dk or k.shape != q.shape or v.shape != (n, n_heads * dv) or out.shape != (n, n_heads * dv)
+                or len({q.dtype, k.dtype, v.dtype}) != 1 or q.dtype not in (torch.float32, self.dtype)):
+            raise KernelError(f"gated_recurrence: q, k, v must be float32 or {self.dtype} and match heads x sizes")
+        if gates.dtype != torch.float32 or out.dtype != torch.float32 or gates.shape != (n, 2 * n_heads if mode == 0 else n_heads * dk):
+            raise KernelError("gated_recurrence: gates and output must be float32 of the kind's shape")
+        if state.dim() != 2 or state.dtype != torch.float32 or not state.is_contiguous() or state.shape[1] < self.recurrence_state_size(kind, n_heads, dk, dv):
+            raise KernelError("gated_recurrence: the state must be contiguous float32 [slots, floats] of the layer's size")
+        ld_b, p_f32 = 0, 0
+        if mode == 1:
+            if beta is None or beta.dtype != torch.float32 or beta.shape != (n, n_heads) or a_log is None or dt_bias is None:
+                raise KernelError("gated_recurrence: the delta rule needs float32 beta [rows, heads], A_log and dt_bias")
+            ld_b = _rows_view(beta, "beta")
+            if a_log.numel() != n_heads or dt_bias.numel() != n_heads * dk or a_log.dtype != dt_bias.dtype or a_log.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("gated_recurrence: A_log per head and dt_bias per head and key channel, one dtype")
+            p_f32 = 1 if a_log.dtype == torch.float32 else 0
+        h = lib("gated_recurrence")
+        _check(h.kvad_gated_recurrence(mode, _code(q.dtype), _ptr(q), ld_q, _ptr(k), ld_k, _ptr(v), ld_v, _ptr(gates), ld_g, _ptr(beta), ld_b,
+                                       _ptr(a_log), _ptr(dt_bias), p_f32, _ptr(out), ld_o, _ptr(state), state.stride(0), _ptr(seq_starts),
+                                       _ptr(seq_slots), int(n_seqs), int(n_heads), int(n_kv_heads), int(dk), int(dv), float(q_scale),
+                                       float(cap), _stream()), h)
+
+    def short_conv(self, x, taps, y, state, conv_off: int, row_seq, row_pos, seq_starts, seq_slots, *, n_sigmoid: int = 0,
+                   unit_heads: int = 0, unit_dim: int = 0, scaled_heads: int = 0, head_scale: float = 1.0, unit_eps: float = 0.0) -> None:
+        """y[:, :C] = silu(causal convolution over time per channel of x[:, :C]) with `taps` [C, n]: the last column meets the
+        row itself, inputs before the step's rows come from the sequence's kept inputs (`state[slot, conv_off:]` as
+        [n - 1, C]), zeros before position 0.  The first `unit_heads` x `unit_dim` channels are then made unit vectors per head
+        (sum of squares + `unit_eps` under the root), the first `scaled_heads` of them times `head_scale`.  The `n_sigmoid`
+        columns after the channels are y = sigmoid(x).  y is float32."""
+        _need_cuda(x, taps, y, state, row_seq, row_pos, seq_starts, seq_slots)
+        ld_x, ld_y = _rows_view(x, "short_conv input"), _rows_view(y, "short_conv output")
+        C, n_taps = taps.shape
+        n = y.shape[0]
+        if (x.dtype != self.dtype or taps.dtype != self.dtype or not taps.is_contiguous() or y.dtype != torch.float32 or x.shape[0] != n
+                or x.shape[1] < C + n_sigmoid or y.shape[1] < C + n_sigmoid or state.dtype != torch.float32 or state.dim() != 2
+                or state.shape[1] < conv_off + (n_taps - 1) * C):
+            raise KernelError(f"short_conv: needs {self.dtype} rows and taps, float32 output and state of matching sizes")
+        h = lib("gated_recurrence")
+        _check(h.kvad_short_conv(self.code, _ptr(x), ld_x, _ptr(taps), _ptr(y), ld_y, _ptr(state), state.stride(0), int(conv_off),
+                                 _ptr(row_seq), _ptr(row_pos), _ptr(seq_starts), _ptr(seq_slots), n, C, n_taps, int(n_sigmoid),
+                                 int(unit_heads), int(unit_dim), int(scaled_heads), float(head_scale), float(unit_eps), _stream()), h)
+
+    def conv_state(self, x, n_channels: int, n_taps: int, state, conv_off: int, seq_starts, seq_slots, n_seqs: int) -> None:
+        """Keeps every sequence's last `n_taps` - 1 rows of x[:, :n_channels] (older ones from what was kept) for the next step."""
+        _need_cuda(x, state, seq_starts, seq_slots)
+        ld_x = _rows_view(x, "conv_state input")
+        if x.dtype != self.dtype or x.shape[1] < n_channels or state.dtype != torch.float32 or state.shape[1] < conv_off + (n_taps - 1) * n_channels:
+            raise KernelError("conv_state: rows of the compute dtype and a float32 state with room for the kept inputs")
+        h = lib("gated_recurrence")
+        _check(h.kvad_conv_state(self.code, _ptr(x), ld_x, _ptr(state), state.stride(0), int(conv_off), _ptr(seq_starts), _ptr(seq_slots),
+                                 int(n_seqs), int(n_channels), int(n_taps), _stream()), h)
+
+    def head_norm_gate(self, raw, gate, weight, out, n_heads: int, eps: float, *, weight_per_head: bool) -> None:
+        """out = raw / sqrt(mean over the head (raw^2) + eps) * weight * sigmoid(gate), head by head; `weight` is as long as
+        all heads (`weight_per_head`) or as one head; `raw` float32, `gate` and `out` of the compute dtype."""
+        _need_cuda(raw, gate, weight, out)
+        ld_r, ld_o = _rows_view(raw, "read-out"), _rows_view(out, "normed read-out")
+        n, total = raw.shape
+        dv = total // n_heads
+        if raw.dtype != torch.float32 or out.dtype != self.dtype or out.shape != raw.shape or dv * n_heads != total:
+            raise KernelError(f"head_norm_gate: float32 input and {self.dtype} output of one shape, whole heads")
+        ld_g = 0
+        if gate is not None:
+            ld_g = _rows_view(gate, "gate")
+            if gate.shape != raw.shape or gate.dtype != self.dtype:
+                raise KernelError("head_norm_gate: the gate must have the output's shape and dtype")
+        w_f32 = 0
+        if weight is not None:
+            if weight.numel() != (total if weight_per_head else dv) or weight.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("head_norm_gate: the weight must be as long as all heads or as one, float32 or bfloat16")
+            w_f32 = 1 if weight.dtype == torch.float32 else 0
+        h = lib("gated_recurrence")
+        _check(h.kvad_head_norm_gate(self.code, _ptr(raw), ld_r, _ptr(gate), ld_g, _ptr(weight), w_f32, int(bool(weight_per_head)), _ptr(out),
+                                     ld_o, n, int(n_heads), dv, float(eps), _stream()), h)
+
+    # -- routed feed-forward ------------------------------------------------------------------
+    def moe_tile_rows(self) -> int:
+        return int(lib("moe").kvad_moe_tile_rows())
+
+    def moe_max_tiles(self, n_rows: int, top: int, n_experts: int) -> int:
+        """How many tiles of positions a step of this shape can need at most, whatever the routing."""
+        slots = n_rows * top
+        return min(slots, slots // self.moe_tile_rows() + n_experts)
+
+    def moe_route(self, logits, top: int, chosen, weight) -> None:
+        """Per row of float32 `logits` [rows, experts]: the `top` largest (ties: the lower index) into int32 `chosen`
+        [rows, top], softmax over the chosen logits into float32 `weight` [rows, top]."""
+        _need_cuda(logits, chosen, weight)
+        n, E = logits.shape
+        if (logits.dtype != torch.float32 or chosen.dtype != torch.int32 or weight.dtype != torch.float32 or chosen.shape != (n, top)
+                or weight.shape != (n, top) or not chosen.is_contiguous() or not weight.is_contiguous()):
+            raise KernelError("moe_route: float32 logits, int32 choices and float32 weights [rows, top]")
+        h = lib("moe")
+        _check(h.kvad_moe_route(_ptr(logits), _rows_view(logits, "router logits"), n, E, int(top), _ptr(chosen), _ptr(weight), _stream()), h)
+
+    def moe_sort(self, chosen, n_experts: int, tile_expert, pos_row, pos_slot) -> None:
+        """Groups the (row, choice) slots of `chosen` [rows, top] by expert, every expert's list padded to whole tiles:
+        `tile_expert` [tiles] (-1: unused), `pos_row` / `pos_slot` [tiles x tile rows] (-1: padding)."""
+        _need_cuda(chosen, tile_expert, pos_row, pos_slot)
+        n, top = chosen.shape
+        tiles = tile_expert.numel()
+        if any(t.dtype != torch.int32 or not t.is_contiguous() for t in (chosen, tile_expert, pos_row, pos_slot)) or \
+                pos_row.numel() < tiles * self.moe_tile_rows() or pos_slot.numel() < tiles * self.moe_tile_rows():
+            raise KernelError("moe_sort: int32 lists, a tile's rows per tile")
+        h = lib("moe")
+        _check(h.kvad_moe_sort(_ptr(chosen), n * top, top, int(n_experts), tiles, _ptr(tile_expert), _ptr(pos_row), _ptr(pos_slot), _stream()), h)
+
+    def grouped_linear(self, a, weight, out, tile_expert, valid, *, in_rows=None, out_rows=None) -> None:
+        """For every tile t of positions and position p in it: out[out_rows[p]] = weight[tile_expert[t]] . a[in_rows[p]]
+        (`weight` [experts, outputs, inputs]; a row list that is None is the position itself; `valid[p]` < 0: padding).
+        `out` is of the compute dtype or float32."""
+        _need_cuda(a, weight, out, tile_expert, valid, in_rows, out_rows)
+        ld_a, ld_o = _rows_view(a, "grouped input"), _rows_view(out, "grouped output")
+        if weight.dim() != 3 or not weight.is_contiguous() or a.dtype != self.dtype or weight.dtype != self.dtype or out.dtype not in (self.dtype, torch.float32):
+            raise KernelError(f"grouped_linear: needs [experts, out, in] weights and rows of {self.dtype}")
+        _, n_out, k = weight.shape
+        if a.shape[1] != k or out.shape[1] != n_out:
+            raise KernelError("grouped_linear: rows do not match the experts' sizes")
+        h = lib("moe")
+        _check(h.kvad_grouped_linear(self.code, 1 if out.dtype == torch.float32 else 0, _ptr(a), ld_a, _ptr(in_rows), _ptr(weight),
+                                     weight.stride(0), _ptr(out), ld_o, _ptr(out_rows), _ptr(valid), _ptr(tile_expert), tile_expert.numel(),
+                                     n_out, k, _stream()), h)
+
+    def clamped_glu(self, gate, up, out, limit: float, alpha: float = 1.702) -> None:
+        """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), 32-bit arithmetic."""
+        _need_cuda(gate, up, out)
+        ld_g, ld_u, ld_o = _rows_view(gate, "gate"), _rows_view(up, "up"), _rows_view(out, "clamped_glu output")
+        if gate.shape != up.shape or out.shape != gate.shape or {gate.dtype, up.dtype, out.dtype} != {self.dtype}:
+            raise KernelError(f"clamped_glu: needs three {self.dtype} tensors of one shape")
+        h = lib("moe")
+        _check(h.kvad_clamped_glu(self.code, _ptr(gate), ld_g, _ptr(up), ld_u, _ptr(out), ld_o, gate.shape[0], gate.shape[1], float(limit),
+                                  float(alpha), _stream()), h)
+
+    def moe_combine(self, residual, slots, weight) -> None:
+        """residual[r] += sum_k weight[r, k] * slots[r * top + k], the choices in order (all float32)."""
+        _need_cuda(residual, slots, weight)
+        n, width = residual.shape
+        top = weight.shape[1]
+        if (any(t.dtype != torch.float32 or not t.is_contiguous() for t in (residual, slots, weight)) or weight.shape[0] != n
+                or slots.shape != (n * top, width)):
+            raise KernelError("moe_combine: float32 stream [rows, width], expert outputs [rows x top, width], weights [rows, top]")
+        h = lib("moe")
+        _check(h.kvad_moe_combine(_ptr(residual), _ptr(slots), _ptr(weight), n, width, top, _stream()), h)
 
     # -- sampling ------------------------------------------------------------------
     ARGMAX_CHUNK = 2048

@@ -1,7 +1,7 @@
 """The two ends of a model: token embedding at the bottom, output head on top.
 
 `token_embedding`: x[r] = table[token[r]] (+ the position encoding's table
-row, if it has one), into the 32-bit residual stream
+row, if it has one; then a norm of its own, if it has one), into the 32-bit residual stream
 (crates/llm/src/model/gpt2.rs:200-213).  `lm_head`: the final norm over the
 rows whose logits are wanted, then one product with the `[vocab, width]`
 matrix - the embedding table itself when the head is tied, so no second copy
@@ -23,14 +23,16 @@ class TokenEmbedding(Part):
     graph_safe = True
 
     def __init__(self, prefix: str, vocab_size: int, width: int, name: str = "wte.weight",
-                 position: Optional[PartSpec] = None):
+                 position: Optional[PartSpec] = None, norm: Optional[PartSpec] = None, norm_name: str = "embed.norm"):
         super().__init__(prefix)
         self.vocab_size, self.width, self.name = int(vocab_size), int(width), name
         self.weight: Optional[torch.Tensor] = None
         self.position = build_part("position", position, prefix) if position is not None else None
+        self.norm = build_part("norm", norm, prefix + norm_name) if norm is not None else None
 
     def children(self):
-        return [self.position] if self.position is not None else []
+        return [p for p in (self.position, self.norm) if p is not None]
+
 
     def own_requests(self):
         return [TensorRequest(self.prefix + self.name, (self.vocab_size, self.width))]
@@ -48,7 +50,12 @@ class TokenEmbedding(Part):
     def forward(self, ctx) -> torch.Tensor:
         x = ctx.buffer((ctx.n_rows, self.width), torch.float32)
         table = self.position.table() if self.position is not None else None
-        ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, x)
+        if self.norm is None:
+            ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, x)
+            return x
+        looked_up = ctx.buffer((ctx.n_rows, self.width), torch.float32)
+        ctx.ops.embed(ctx.tokens, ctx.row_pos, self.weight, table, looked_up)
+        self.norm.forward(ctx, looked_up, n_rows=ctx.n_rows, out=x)       # (the stream stays 32-bit)
         return x
 
 

@@ -58,32 +58,56 @@ class Linear(Part):
 
 
 class FusedLinear(Part):
-    """Several bias-free linear maps of one input, stored as tensors of their own (`[out, in]` each) and held
-    as ONE matrix, rows one map after another: one product gives all of them, each a range of columns of the
-    output (`columns(i)`)."""
+    """Several linear maps of one input, stored as tensors of their own (`[out, in]` each) and held as ONE
+    matrix, rows one map after another: one product gives all of them, each a range of columns of the output
+    (`columns(i)`).  A map given as (name, size, align) starts at a column that is a multiple of `align` (rows of
+    zeros fill the gap), `pad_to` rounds the whole up the same way; with `bias_suffix` every map has a bias
+    tensor `<name><bias_suffix>`."""
     graph_safe = True
 
-    def __init__(self, prefix: str, in_features: int, parts):
+    def __init__(self, prefix: str, in_features: int, parts, pad_to: int = 1, bias_suffix: Optional[str] = None):
         super().__init__(prefix)
         self.in_features = int(in_features)
-        self.names = [str(n) for n, _ in parts]
-        self.sizes = [int(o) for _, o in parts]
-        self.out_features = sum(self.sizes)
+        self.names = [str(p[0]) for p in parts]
+        self.sizes = [int(p[1]) for p in parts]
+        self.offsets = []
+        at = 0
+        for p, size in zip(parts, self.sizes):
+            align = int(p[2]) if len(p) > 2 else 1
+            at = -(-at // align) * align
+            self.offsets.append(at)
+            at += size
+        self.out_features = -(-at // int(pad_to)) * int(pad_to)
+        self.bias_suffix = bias_suffix
         self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
 
     def own_requests(self):
-        return [TensorRequest(self.prefix + n, (o, self.in_features)) for n, o in zip(self.names, self.sizes)]
+        out = [TensorRequest(self.prefix + n, (o, self.in_features)) for n, o in zip(self.names, self.sizes)]
+        if self.bias_suffix is not None:
+            out += [TensorRequest(self.prefix + n + self.bias_suffix, (o,)) for n, o in zip(self.names, self.sizes)]
+        return out
 
     def load_own(self, fetch):
-        self.weight = torch.cat([fetch(self.prefix + n) for n in self.names], dim=0).contiguous()
+        mats = [fetch(self.prefix + n) for n in self.names]
+        if self.out_features == sum(self.sizes):
+            self.weight = torch.cat(mats, dim=0).contiguous()
+        else:
+            self.weight = torch.zeros((self.out_features, self.in_features), dtype=mats[0].dtype, device=mats[0].device)
+            for m, lo in zip(mats, self.offsets):
+                self.weight[lo:lo + m.shape[0]] = m
+        if self.bias_suffix is not None:
+            vecs = [fetch(self.prefix + n + self.bias_suffix, keep_f32=True).float() for n in self.names]
+            self.bias = torch.zeros(self.out_features, dtype=torch.float32, device=vecs[0].device)
+            for b, lo in zip(vecs, self.offsets):
+                self.bias[lo:lo + b.numel()] = b
 
     def own_tensors(self):
-        return [self.weight]
+        return [t for t in (self.weight, self.bias) if t is not None]
 
     def columns(self, i: int) -> slice:
-        lo = sum(self.sizes[:i])
-        return slice(lo, lo + self.sizes[i])
+        return slice(self.offsets[i], self.offsets[i] + self.sizes[i])
 
     def forward(self, ctx, a, out: torch.Tensor, epilogue: str = "store") -> torch.Tensor:
-        ctx.ops.linear(a, self.weight, None, out, epilogue)
+        ctx.ops.linear(a, self.weight, self.bias, out, epilogue)
         return out

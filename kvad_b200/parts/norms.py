@@ -69,9 +69,11 @@ class RMSNorm(Norm):
     def own_tensors(self):
         return [self.weight] if self.weight is not None else []
 
-    def forward(self, ctx, x, rows=None, n_rows=None):
+    def forward(self, ctx, x, rows=None, n_rows=None, out=None):
+        """`out`: where to write (None: a new buffer of the compute dtype; a 32-bit one keeps a 32-bit input's precision)."""
         n = n_rows if n_rows is not None else (x.shape[0] if rows is None else rows.numel())
-        out = ctx.buffer((n, self.width))
+        if out is None:
+            out = ctx.buffer((n, self.width))
         deferred = ctx.shared.get("deferred_residual") if x.dtype == torch.float32 else None
         if deferred is not None and deferred[0] is not x:
             deferred = None

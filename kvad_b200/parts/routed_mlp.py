@@ -1,0 +1,110 @@
+"""Feed-forwards with clamped gates, alone or as a mixture of experts.
+
+`clamped_glu_mlp`: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g sigmoid(alpha g) (u + 1), out = W_down y;
+no biases.  Gate and up run as one product, the activation as one row-wise kernel, the residual sum in the last
+product's epilogue.
+
+`routed_mlp`: `n_experts` such feed-forwards (`e0`, `e1`, ...), of which every row uses `top`: router logits
+z = W_router h + b in 32-bit, the `top` largest are chosen, their weights are the softmax over the chosen logits only,
+the output is the weighted sum of the chosen experts' outputs; an optional shared expert (`shared`, the same form with
+sizes of its own) runs for every row and is added.  The (row, choice) pairs are grouped by expert on the device and
+the experts' two products run as grouped products over those lists (`csrc/moe.cu`); how many tiles a step can need
+follows from its shape alone, so the launches never depend on the routing.  The chosen experts' outputs are summed
+choice by choice in a fixed order.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..weights.source import TensorRequest
+from .base import FeedForward, register_part
+from .linear import FusedLinear, Linear
+
+
+class ClampedGluMLP(FeedForward):
+    graph_safe = True
+    kernel_families = ("moe",)
+
+    def __init__(self, prefix: str, width: int, hidden: int, limit: float, alpha: float = 1.702, gate_name: str = "gate",
+                 up_name: str = "up", down_name: str = "down"):
+        super().__init__(prefix)
+        self.width, self.hidden, self.limit, self.alpha = int(width), int(hidden), float(limit), float(alpha)
+        self.gate_up = FusedLinear(prefix, self.width, [(gate_name, self.hidden, 8), (up_name, self.hidden, 8)], pad_to=8)
+        self.down = Linear(prefix + down_name, self.hidden, self.width, bias=False, weight_name="")
+
+    def children(self):
+        return [self.gate_up, self.down]
+
+    def forward(self, ctx, h, residual):
+        n = h.shape[0]
+        both = ctx.buffer((n, self.gate_up.out_features))
+        self.gate_up.forward(ctx, h, both)
+        hid = ctx.buffer((n, self.hidden))
+        ctx.ops.clamped_glu(both[:, self.gate_up.columns(0)], both[:, self.gate_up.columns(1)], hid, self.limit, self.alpha)
+        self.down.forward(ctx, hid, residual, "residual")
+
+
+class RoutedMLP(FeedForward):
+    graph_safe = True
+    kernel_families = ("moe",)
+
+    def __init__(self, prefix: str, width: int, n_experts: int, top: int, hidden: int, limit: float, alpha: float = 1.702,
+                 shared: Optional[dict] = None, router_name: str = "router", router_bias_name: str = ".b", expert_name: str = "e{}.",
+                 shared_name: str = "shared.", gate_name: str = "gate", up_name: str = "up", down_name: str = "down"):
+        super().__init__(prefix)
+        self.width, self.n_experts, self.top, self.hidden = int(width), int(n_experts), int(top), int(hidden)
+        if not (1 <= self.top <= self.n_experts):
+            raise ValueError(f"routed_mlp: every row uses {top} of {n_experts} experts")
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.router = Linear(prefix + router_name, self.width, self.n_experts, bias=True, weight_name="", bias_name=router_bias_name)
+        self.shared = ClampedGluMLP(prefix + shared_name, self.width, **shared) if shared else None
+        self.names = dict(expert=expert_name, gate=gate_name, up=up_name, down=down_name)
+        self.w_in = None           # [experts, 2 hidden, width]: every expert's gate rows, then its up rows
+        self.w_out = None          # [experts, width, hidden]
+
+    def children(self):
+        return [self.router] + ([self.shared] if self.shared is not None else [])
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.prefix + self.names["expert"].format(e) + self.names[which]
+
+    def own_requests(self):
+        out = []
+        for e in range(self.n_experts):
+            out += [TensorRequest(self._expert(e, "gate"), (self.hidden, self.width)), TensorRequest(self._expert(e, "up"), (self.hidden, self.width)),
+                    TensorRequest(self._expert(e, "down"), (self.width, self.hidden))]
+        return out
+
+    def load_own(self, fetch):
+        self.w_in = torch.stack([torch.cat([fetch(self._expert(e, "gate")), fetch(self._expert(e, "up"))], dim=0)
+                                 for e in range(self.n_experts)]).contiguous()
+        self.w_out = torch.stack([fetch(self._expert(e, "down")) for e in range(self.n_experts)]).contiguous()
+
+    def own_tensors(self):
+        return [t for t in (self.w_in, self.w_out) if t is not None]
+
+    def forward(self, ctx, h, residual):
+        n, ops, E, top, ff = h.shape[0], ctx.ops, self.n_experts, self.top, self.hidden
+        logits = ctx.buffer((n, (E + 3) // 4 * 4), torch.float32)[:, :E]
+        self.router.forward(ctx, h, logits, "store_f32")
+        chosen, weight = ctx.buffer((n, top), torch.int32), ctx.buffer((n, top), torch.float32)
+        ops.moe_route(logits, top, chosen, weight)
+        tiles, tm = ops.moe_max_tiles(n, top, E), ops.moe_tile_rows()
+        tile_expert = ctx.buffer((tiles,), torch.int32)
+        pos_row, pos_slot = ctx.buffer((tiles * tm,), torch.int32), ctx.buffer((tiles * tm,), torch.int32)
+        ops.moe_sort(chosen, E, tile_expert, pos_row, pos_slot)
+        both = ctx.buffer((tiles * tm, 2 * ff))
+        ops.grouped_linear(h, self.w_in, both, tile_expert, pos_slot, in_rows=pos_row)
+        hid = ctx.buffer((tiles * tm, ff))
+        ops.clamped_glu(both[:, :ff], both[:, ff:], hid, self.limit, self.alpha)
+        outs = ctx.buffer((n * top, self.width), torch.float32)
+        ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot, out_rows=pos_slot)
+        ops.moe_combine(residual, outs, weight)
+        if self.shared is not None:
+            self.shared.forward(ctx, h, residual)
+
+
+register_part("feed_forward", "clamped_glu_mlp", ClampedGluMLP)
+register_part("feed_forward", "routed_mlp", RoutedMLP)
