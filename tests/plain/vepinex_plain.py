@@ -84,25 +84,35 @@ def rotate_pairs(x, positions, base, dims):
 
 
 # ----------------------------------------------------------------------------- mixers
+def gate_caps(a, b, cap):
+    """Log input gate and log forget gate from the two gate projections."""
+    return cap * np.tanh(a / cap), logsigmoid(cap * np.tanh(b / cap))
+
+
+def matrix_memory_cell(q, k, v, gi, gf, state=None):
+    """One head, token by token: q, k [T, dk], v [T, dv], log gates gi, gf [T].  Returns (read-outs [T, dv], state);
+    the state is (S [dk, dv], n [dk], m) and starts at zero, the running maximum too."""
+    S, n, mx = state if state is not None else (np.zeros((q.shape[1], v.shape[1])), np.zeros(q.shape[1]), 0.0)
+    out = np.zeros(v.shape)
+    for t in range(q.shape[0]):
+        new = max(gf[t] + mx, gi[t])
+        keep, take = math.exp(gf[t] + mx - new), math.exp(gi[t] - new)
+        S = keep * S + take * np.outer(k[t], v[t])
+        n = keep * n + take * k[t]
+        mx = new
+        out[t] = (S.T @ q[t]) / (max(abs(n @ q[t]), math.exp(-mx)) + 1e-6)
+    return out, (S, n, mx)
+
+
 def mlstm(h, w, p, m, eps):
-    """Matrix memory, token by token.  h [T, width]; returns [T, width]."""
+    """Matrix memory.  h [T, width]; returns [T, width]."""
     T = h.shape[0]
     H, dk, dv, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
     q = (h @ w[p + "q"].T).reshape(T, H, dk) * dk ** -0.5
     k = (h @ w[p + "k"].T).reshape(T, H, dk)
     v = (h @ w[p + "v"].T).reshape(T, H, dv)
-    gi = cap * np.tanh((h @ w[p + "i"].T + w[p + "i.b"]) / cap)
-    gf = logsigmoid(cap * np.tanh((h @ w[p + "f"].T + w[p + "f.b"]) / cap))
-    out = np.zeros((T, H, dv))
-    for a in range(H):
-        S, n, mx = np.zeros((dk, dv)), np.zeros(dk), 0.0
-        for t in range(T):
-            new = max(gf[t, a] + mx, gi[t, a])
-            keep, take = math.exp(gf[t, a] + mx - new), math.exp(gi[t, a] - new)
-            S = keep * S + take * np.outer(k[t, a], v[t, a])
-            n = keep * n + take * k[t, a]
-            mx = new
-            out[t, a] = (S.T @ q[t, a]) / (max(abs(n @ q[t, a]), math.exp(-mx)) + 1e-6)
+    gi, gf = gate_caps(h @ w[p + "i"].T + w[p + "i.b"], h @ w[p + "f"].T + w[p + "f.b"], cap)
+    out = np.stack([matrix_memory_cell(q[:, a], k[:, a], v[:, a], gi[:, a], gf[:, a])[0] for a in range(H)], axis=1)
     o = rms_unit(out, eps).reshape(T, H * dv) * w[p + "norm"] * sigmoid(h @ w[p + "g"].T)
     return o @ w[p + "o"].T
 
@@ -140,27 +150,38 @@ def short_conv(x, taps):
     return sum(padded[j:j + T] * taps[:, j][None, :] for j in range(n))
 
 
+def unit_vectors(x, eps=1e-6):
+    return x / np.sqrt((x * x).sum(-1, keepdims=True) + eps)
+
+
+def channel_decay(a, a_log, dt_bias):
+    """a [T, H, dk] raw, A_log [H], dt_bias [H, dk] -> the decay of every key channel."""
+    return np.exp(-np.exp(a_log)[None, :, None] * softplus(a + dt_bias[None]))
+
+
+def delta_cell(q, k, v, beta, g, S=None):
+    """One head, token by token: q, k, g [T, dk], v [T, dv], beta [T].  Returns (read-outs [T, dv], S [dk, dv])."""
+    S = np.zeros((q.shape[1], v.shape[1])) if S is None else S
+    out = np.zeros(v.shape)
+    for t in range(q.shape[0]):
+        S = g[t][:, None] * S
+        u = beta[t] * (v[t] - S.T @ k[t])
+        S = S + np.outer(k[t], u)
+        out[t] = S.T @ q[t]
+    return out, S
+
+
 def channel_delta(h, w, p, m, eps):
-    """The delta rule with a decay per key channel, token by token."""
+    """The delta rule with a decay per key channel."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = silu(short_conv(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(T, G, dk)
     k = silu(short_conv(h @ w[p + "k"].T, w[p + "k.conv"])).reshape(T, G, dk)
     v = silu(short_conv(h @ w[p + "v"].T, w[p + "v.conv"])).reshape(T, H, dv)
-    q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) * dk ** -0.5
-    k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
+    q, k = unit_vectors(q) * dk ** -0.5, unit_vectors(k)
     beta = sigmoid(h @ w[p + "b"].T)
-    a = ((h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]).reshape(T, H, dk)
-    g = np.exp(-np.exp(w[p + "A_log"])[None, :, None] * softplus(a))
-    out = np.zeros((T, H, dv))
-    for a_ in range(H):
-        kv = a_ // (H // G)
-        S = np.zeros((dk, dv))
-        for t in range(T):
-            S = g[t, a_][:, None] * S
-            u = beta[t, a_] * (v[t, a_] - S.T @ k[t, kv])
-            S = S + np.outer(k[t, kv], u)
-            out[t, a_] = S.T @ q[t, kv]
+    g = channel_decay(((h @ w[p + "a1"].T) @ w[p + "a2"].T).reshape(T, H, dk), w[p + "A_log"], w[p + "dt_bias"].reshape(H, dk))
+    out = np.stack([delta_cell(q[:, a // (H // G)], k[:, a // (H // G)], v[:, a], beta[:, a], g[:, a])[0] for a in range(H)], axis=1)
     gate = sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T).reshape(T, H, dv)
     o = rms_unit(out, eps) * w[p + "norm"][None, None, :] * gate
     return o.reshape(T, H * dv) @ w[p + "o"].T
@@ -171,21 +192,42 @@ def dense_ff(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
+def clamped_glu(gate, up, limit):
+    g, u = np.minimum(gate, limit), np.clip(up, -limit, limit)
+    return g * sigmoid(1.702 * g) * (u + 1.0)
+
+
 def clamped_expert(h, w, p, limit):
-    g = np.minimum(h @ w[p + "gate"].T, limit)
-    u = np.clip(h @ w[p + "up"].T, -limit, limit)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
+    return clamped_glu(h @ w[p + "gate"].T, h @ w[p + "up"].T, limit) @ w[p + "down"].T
 
 
-def route(h, w, p, top):
-    """(chosen experts [T, top], their weights [T, top]): the largest logits, softmax over the chosen only."""
-    z = h @ w[p + "router"].T + w[p + "router.b"]
+def choose(z, top):
+    """(chosen experts [T, top], their weights [T, top]): the largest logits (ties: the lower index), softmax over the chosen only."""
     chosen = np.argsort(-z, axis=-1, kind="stable")[:, :top]
     return chosen, softmax_rows(np.take_along_axis(z, chosen, -1))
 
 
-def moe_ff(h, w, p, mlp):
+def route(h, w, p, top):
+    return choose(h @ w[p + "router"].T + w[p + "router.b"], top)
+
+
+def routing_margin(h, w, p, top):
+    """Per row, how far the last chosen logit is above the first one left out (infinite where all are chosen)."""
+    z = np.sort(h @ w[p + "router"].T + w[p + "router.b"], axis=-1)[:, ::-1]
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else np.full(h.shape[0], np.inf)
+
+
+def moe_ff(h, w, p, mlp, margins=None, forced=None, own=None):
+    """`forced` [T, top]: these experts instead of the router's own choice (their weights still from its logits);
+    `own`: a list that receives the router's own choice."""
     chosen, weight = route(h, w, p, mlp["router"]["top"])
+    if own is not None:
+        own.append(chosen)
+    if forced is not None:
+        chosen = np.asarray(forced)
+        weight = softmax_rows(np.take_along_axis(h @ w[p + "router"].T + w[p + "router.b"], chosen, -1))
+    if margins is not None:
+        margins.append(routing_margin(h, w, p, mlp["router"]["top"]))
     out = np.zeros((h.shape[0], w[p + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t], weight[t]):
@@ -196,8 +238,11 @@ def moe_ff(h, w, p, mlp):
 
 
 # ----------------------------------------------------------------------------- the model
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and the stream after every layer, if asked)."""
+def forward(config, w, tokens, return_layers=False, margins=None, forced=None, own=None):
+    """Logits [T, vocab] of one whole sequence (and the stream after every layer, if asked).  `margins`: a list that
+    receives, per routed layer, every row's routing margin.  `forced`: per routed layer, the experts [T, top] to use;
+    `own`: a list that receives, per routed layer, what its router chose by itself given the layers before it."""
+    forced = list(forced) if forced is not None else None
     eps = config["norm"]["eps"]
     positions = np.arange(len(tokens))
     x = rms_unit(w["embed"][np.asarray(tokens)], eps) * w["embed.norm"]
@@ -219,11 +264,18 @@ def forward(config, w, tokens, return_layers=False):
             raise ValueError(layer["type"])
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = y + (dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp))
+            y = y + (dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp, margins, forced.pop(0) if forced else None, own))
         x = x + y
         after.append(x.copy())
     logits = (rms_unit(x, eps) * w["final.norm"]) @ w["embed"].T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+def greedy(config, w, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(forward(config, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
 
 
 def load(model_dir):
