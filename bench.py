@@ -255,22 +255,39 @@ def nifulix_config(width, ff, vocab, heads, dim, window):
     return {"architecture": "Nifulix", "vocab": vocab, "width": width, "residual_mult": 0.3, "norm": {"eps": 1e-5}, "layers": layers}
 
 
+def vepinex_config(width, ff, vocab, heads, dim):
+    """Layers that resemble a real model's: two of each kind of mixer (the second latent layer reads the first one's cache), a routed
+    feed-forward in every layer whose two chosen experts and shared expert together are as wide as the dense `ff`."""
+    mem = {"type": "mlstm", "mixer": {"heads": width // 128, "dim": 64, "vdim": 128, "gate_cap": 15.0}}
+    dlt = {"type": "channel_delta", "mixer": {"heads": width // 128, "kv_heads": width // 128, "dim": 128, "vdim": 128, "conv": 4,
+                                              "decay_rank": width // 16, "gate_rank": width // 16}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": width // 4,
+                                                 "scale": (1.5 * dim) ** -0.5, "rot": {"base": 5e4, "dims": dim // 2}}}
+    lat2 = {"type": "latent_attention", "mixer": dict(lat["mixer"], kv_from=1)}
+    mlp = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 2, "limit": 7.0}}
+    return {"architecture": "Vepinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [dict(l, mlp=mlp) for l in (mem, lat, dlt, mem, lat2, dlt)]}
+
+
 def design_points(args, pk, pk_src):
     """`--design nifulix`: prefill and decode throughput of Nifulix at layer sizes that resemble a real model's, beside GPT-2 (the
     closest model this library runs) at the same width, depth, head size and weight count of the feed-forward; and, from
-    a kernel-by-kernel pass with CUDA events around every operation, each design's mean time per operation."""
+    a kernel-by-kernel pass with CUDA events around every operation, each design's mean time per operation.
+    `--design vepinex`: the same for Vepinex beside Nifulix (recurrent, latent-attention and gated feed-forward layers of its own)."""
     import torch
     from kvad_b200 import StepEntry, profile, write_random_model
 
     sizes = {"w1024": dict(width=1024, heads=16, dim=64, ff=2816, inner=4096), "w2048": dict(width=2048, heads=16, dim=128, ff=5632, inner=8192)}
     vocab, ctx, window, plen = 32000, 2048, 512, 512
-    out = {"design": "nifulix", "beside": "gpt2", "dtype": args.dtype, "data": "synthetic: seeded uniform-random token ids, seeded random weights",
+    first, second = ("nifulix", "gpt2") if args.design == "nifulix" else ("vepinex", "nifulix")
+    out = {"design": first, "beside": second, "dtype": args.dtype, "data": "synthetic: seeded uniform-random token ids, seeded random weights",
            "prefill": "one step of 2 x 1024 prompt tokens, L2 flushed between iterations", "decode": f"batch {args.batch}, {plen}-token prompts, {min(args.steps, 128)} steps after {max(3, args.warmup)} warm-up steps, tokens fed back on the device",
            "window": window, "sizes": {}}
     for name, z in sizes.items():
         row = {}
-        for design in ("nifulix", "gpt2"):
-            cfg = (nifulix_config(z["width"], z["ff"], vocab, z["heads"], z["dim"], window) if design == "nifulix" else
+        for design in (first, second):
+            cfg = (vepinex_config(z["width"], z["ff"], vocab, z["heads"], z["dim"]) if design == "vepinex" else
+                   nifulix_config(z["width"], z["ff"], vocab, z["heads"], z["dim"], window) if design == "nifulix" else
                    dict(model_type="gpt2", n_layer=6, n_embd=z["width"], n_head=z["heads"], n_inner=z["inner"], vocab_size=vocab, n_positions=ctx,
                         layer_norm_epsilon=1e-5, activation_function="gelu_new"))
             with tempfile.TemporaryDirectory(prefix="kvad_b200-bench-") as d:
@@ -375,8 +392,9 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="the same as --points none")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "sampled"],
                     help="`sampled`: the timed decode steps draw with temperature 0.7, top-k 40, top-p 0.95")
-    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix"],
-                    help="`nifulix`: instead of the headline, Nifulix beside GPT-2 at equal sizes (prefill, decode, time per operation)")
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "nifulix", "vepinex"],
+                    help="`nifulix`: instead of the headline, Nifulix beside GPT-2 at equal sizes (prefill, decode, time per operation); "
+                         "`vepinex`: Vepinex beside Nifulix")
     args = ap.parse_args()
     if args.skip_points:
         args.points = "none"
@@ -402,7 +420,7 @@ def main():
     from kvad_b200 import write_random_model
 
     pk, pk_src = peaks()
-    if args.design == "nifulix":
+    if args.design in ("nifulix", "vepinex"):
         return design_points(args, pk, pk_src)
     tmp = tempfile.TemporaryDirectory(prefix="kvad_b200-bench-")
     model_dir = tmp.name

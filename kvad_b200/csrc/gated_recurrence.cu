@@ -50,15 +50,23 @@ struct RecArgs {
 template <typename TI, int EPL, int MODE>
 __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   constexpr int DKP = EPL * 8, TC = EPL >= 32 ? 8 : 16;
+  constexpr int PER = TC * DKP / 128;          // staged q (k, gate) entries a thread carries from global to shared memory
+  constexpr int VPER = TC * COLS / 128;
   __shared__ float sq[TC][DKP], sk[TC][DKP];
   __shared__ float sg[MODE == 1 ? TC : 1][MODE == 1 ? DKP : 1];
+  __shared__ float sbias[MODE == 1 ? DKP : 1];
   __shared__ float sv[TC][COLS];
-  __shared__ float s_a[TC], s_b[TC], s_c[TC];
+  __shared__ float s_a[TC], s_b[TC], s_c[TC], s_i[TC], s_f[TC];
   __shared__ float s_m;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = lane & 7, grp = lane >> 3;
   const int col = blockIdx.x * COLS + warp * 4 + grp;
   const int h = blockIdx.y, s = blockIdx.z, qh = h / p.group;
   const int dk = p.dk, dv = p.dv;
+  float decay_rate = 0.f;
+  if (MODE == 1) {                             // parameters do not depend on the kernel before
+    decay_rate = expf(load_param(p.a_log, h, p.params_f32));
+    for (int d = tid; d < DKP; d += 128) sbias[d] = d < dk ? load_param(p.dt_bias, h * dk + d, p.params_f32) : 0.f;
+  }
   pdl_launch_dependents();
   pdl_wait();
   const int row0 = p.seq_starts[s], row1 = p.seq_starts[s + 1];
@@ -78,50 +86,62 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   const TI* q = reinterpret_cast<const TI*>(p.q);
   const TI* k = reinterpret_cast<const TI*>(p.k);
   const TI* v = reinterpret_cast<const TI*>(p.v);
-  float decay_rate = 0.f;
-  if (MODE == 1) decay_rate = expf(load_param(p.a_log, h, p.params_f32));
+
+  // the next rows' inputs are fetched into registers while the rows before them are walked
+  float rq[PER], rk[PER], rg[MODE == 1 ? PER : 1], rv[VPER], r0 = 0.f, r1 = 0.f;
+  auto fetch = [&](int c0) {
+    const int nt = min(TC, row1 - c0);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = tid + j * 128, t = i / DKP, d = i - t * DKP;
+      const int64_t r = c0 + t;
+      const bool ok = t < nt && d < dk;
+      rq[j] = ok ? to_f32(q[r * p.ld_q + qh * dk + d]) : 0.f;
+      rk[j] = ok ? to_f32(k[r * p.ld_k + qh * dk + d]) : 0.f;
+      if (MODE == 1) rg[j] = ok ? p.gates[r * p.ld_gates + h * dk + d] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < VPER; ++j) {
+      const int i = tid + j * 128, t = i / COLS, c = blockIdx.x * COLS + (i - t * COLS);
+      rv[j] = (t < nt && c < dv) ? to_f32(v[(int64_t)(c0 + t) * p.ld_v + h * dv + c]) : 0.f;
+    }
+    if (tid < nt) {
+      if (MODE == 1) {
+        r0 = p.beta[(int64_t)(c0 + tid) * p.ld_beta + h];
+      } else {
+        const float* gr = p.gates + (int64_t)(c0 + tid) * p.ld_gates;
+        r0 = gr[h];
+        r1 = gr[p.heads + h];
+      }
+    }
+  };
+  if (row0 < row1) fetch(row0);
 
   for (int c0 = row0; c0 < row1; c0 += TC) {
     const int nt = min(TC, row1 - c0);
-    __syncthreads();
-    for (int i = tid; i < nt * DKP; i += 128) {
-      const int t = i / DKP, d = i - t * DKP;
-      const int64_t r = c0 + t;
-      float qv = 0.f, kv = 0.f, gv = 1.f;
-      if (d < dk) {
-        qv = to_f32(q[r * p.ld_q + qh * dk + d]) * p.q_scale;
-        kv = to_f32(k[r * p.ld_k + qh * dk + d]);
-        if (MODE == 1) {
-          const float a = p.gates[r * p.ld_gates + h * dk + d] + load_param(p.dt_bias, h * dk + d, p.params_f32);
-          gv = expf(-decay_rate * softplus_f(a));
-        }
-      }
-      sq[t][d] = qv;
-      sk[t][d] = kv;
-      if (MODE == 1) sg[t][d] = gv;
+    __syncthreads();                            // the rows before have been walked
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = tid + j * 128, t = i / DKP, d = i - t * DKP;
+      sq[t][d] = rq[j] * p.q_scale;
+      sk[t][d] = rk[j];
+      if (MODE == 1) sg[t][d] = d < dk ? expf(-decay_rate * softplus_f(rg[j] + sbias[d])) : 1.f;
     }
-    for (int i = tid; i < nt * COLS; i += 128) {
-      const int t = i / COLS, j = i - t * COLS, c = blockIdx.x * COLS + j;
-      sv[t][j] = c < dv ? to_f32(v[(int64_t)(c0 + t) * p.ld_v + h * dv + c]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < VPER; ++j) {
+      const int i = tid + j * 128;
+      sv[i / COLS][i % COLS] = rv[j];
     }
-    if (MODE == 1) {
-      if (tid < nt) s_a[tid] = p.beta[(int64_t)(c0 + tid) * p.ld_beta + h];
-    } else if (tid == 0) {
-      float m = s_m;
-      for (int t = 0; t < nt; ++t) {
-        const float* gr = p.gates + (int64_t)(c0 + t) * p.ld_gates;
-        const float ig = p.cap * tanhf(gr[h] / p.cap);
-        const float fc = p.cap * tanhf(gr[p.heads + h] / p.cap);
-        const float fg = -softplus_f(-fc);
-        const float mn = fmaxf(fg + m, ig);
-        s_a[t] = expf(fg + m - mn);
-        s_b[t] = expf(ig - mn);
-        s_c[t] = expf(-mn);
-        m = mn;
+    if (tid < nt) {
+      if (MODE == 1) {
+        s_a[tid] = r0;
+      } else {                                  // the caps and the logarithm of the forget gate, a thread per row
+        s_i[tid] = p.cap * tanhf(r0 / p.cap);
+        s_f[tid] = -softplus_f(-p.cap * tanhf(r1 / p.cap));
       }
-      s_m = m;
     }
     __syncthreads();
+    if (c0 + TC < row1) fetch(c0 + TC);
     if (MODE == 1) {
       for (int t = warp; t < nt; t += 4) {
         float acc = 0.f;
@@ -129,8 +149,26 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
         acc = warp_sum(acc);
         if (lane == 0) s_b[t] = acc;
       }
+    } else {
+      if (tid == 0) {                           // the running maximum is the one thing that goes row by row
+        float m = s_m;
+        for (int t = 0; t < nt; ++t) {
+          const float mn = fmaxf(s_f[t] + m, s_i[t]);
+          s_a[t] = m;
+          s_c[t] = mn;
+          m = mn;
+        }
+        s_m = m;
+      }
       __syncthreads();
+      if (tid < nt) {
+        const float m_before = s_a[tid], mn = s_c[tid];
+        s_a[tid] = expf(s_f[tid] + m_before - mn);
+        s_b[tid] = expf(s_i[tid] - mn);
+        s_c[tid] = expf(-mn);
+      }
     }
+    __syncthreads();
     for (int t = 0; t < nt; ++t) {
       const float vj = sv[t][warp * 4 + grp];
       float a = 0.f, b = 0.f, o;

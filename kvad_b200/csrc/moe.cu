@@ -88,12 +88,45 @@ moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_expe
   }
 }
 
-// Tile of 32 positions x 64 outputs, 256 threads, a thread 2 x 4 outputs; K in steps of 32 through shared memory.
+// Tile of 32 positions x 64 outputs, 256 threads, a thread 2 x 4 outputs; K in steps of 32 through shared memory, the next
+// step's pieces on their way into registers while this one is multiplied (16-byte pieces where `vec` says the sizes and
+// addresses allow).  A warp whose four positions are all padding stages its share and skips the arithmetic: with a few
+// rows a step (decoding) most of a tile is padding and the kernel is a stream of the chosen experts' weights.
+template <typename T, int N> struct Piece;
+template <> struct Piece<float, 4> { using type = float4; };
+template <> struct Piece<__nv_bfloat16, 4> { using type = uint2; };
+template <> struct Piece<__nv_bfloat16, 8> { using type = uint4; };
+
+template <typename T, int N>
+__device__ __forceinline__ void load_piece(const T* p, int n_left, bool vec, float* f) {
+  if (vec && n_left >= N) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int j = 0; j < N; j += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p + j);
+        f[j] = v.x; f[j + 1] = v.y; f[j + 2] = v.z; f[j + 3] = v.w;
+      }
+    } else {
+      const typename Piece<T, N>::type raw = *reinterpret_cast<const typename Piece<T, N>::type*>(p);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < N / 2; ++j) {
+        const float2 v = __bfloat1622float2(h2[j]);
+        f[2 * j] = v.x;
+        f[2 * j + 1] = v.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) f[j] = j < n_left ? to_f32(p[j]) : 0.f;
+  }
+}
+
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 grouped_linear_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict__ in_rows, const T* __restrict__ w,
                       int64_t expert_stride, TO* __restrict__ out, int64_t ld_out, const int* __restrict__ out_rows,
-                      const int* __restrict__ valid, const int* __restrict__ tile_expert, int n_out, int k_dim) {
+                      const int* __restrict__ valid, const int* __restrict__ tile_expert, int n_out, int k_dim, int vec) {
   __shared__ __align__(16) float As[TK][TM + 2];
   __shared__ __align__(16) float Ws[TK][TN + 4];
   __shared__ int rows_in[TM], rows_out[TM];
@@ -111,27 +144,44 @@ grouped_linear_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restri
   __syncthreads();
   const T* we = w + (int64_t)expert * expert_stride;
   const int ty = tid >> 4, tx = tid & 15;
+  const int warp_row = (tid >> 5) * 4;
+  const bool busy = rows_out[warp_row] >= 0 || rows_out[warp_row + 1] >= 0 || rows_out[warp_row + 2] >= 0 || rows_out[warp_row + 3] >= 0;
+  // staging shares: a thread carries 4 entries of one position's row and 8 entries of one output's weights
+  const int am = tid >> 3, ak = (tid & 7) * 4, wn = tid >> 2, wk = (tid & 3) * 8;
+  const int a_row = rows_in[am];
+  const T* a_ptr = a_row >= 0 ? a + (int64_t)a_row * ld_a : nullptr;
+  const T* w_ptr = n0 + wn < n_out ? we + (int64_t)(n0 + wn) * k_dim : nullptr;
+  float ra[4], rw[8];
+  auto fetch = [&](int k0) {
+    if (a_ptr != nullptr) load_piece<T, 4>(a_ptr + k0 + ak, k_dim - k0 - ak, vec != 0, ra);
+    else ra[0] = ra[1] = ra[2] = ra[3] = 0.f;
+    if (w_ptr != nullptr) load_piece<T, 8>(w_ptr + k0 + wk, k_dim - k0 - wk, vec != 0, rw);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) rw[j] = 0.f;
+    }
+  };
+  fetch(0);
   float acc[2][4] = {};
   for (int k0 = 0; k0 < k_dim; k0 += TK) {
-    for (int i = tid; i < TM * TK; i += 256) {
-      const int m = i / TK, kk = i - m * TK, r = rows_in[m];
-      As[kk][m] = (r >= 0 && k0 + kk < k_dim) ? to_f32(a[(int64_t)r * ld_a + k0 + kk]) : 0.f;
-    }
-    for (int i = tid; i < TN * TK; i += 256) {
-      const int n = i / TK, kk = i - n * TK;
-      Ws[kk][n] = (n0 + n < n_out && k0 + kk < k_dim) ? to_f32(we[(int64_t)(n0 + n) * k_dim + k0 + kk]) : 0.f;
-    }
     __syncthreads();
 #pragma unroll
-    for (int kk = 0; kk < TK; ++kk) {
-      const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
-      const float4 b = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
-      acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);
-      acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
-      acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]);
-      acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
-    }
+    for (int j = 0; j < 4; ++j) As[ak + j][am] = ra[j];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) Ws[wk + j][wn] = rw[j];
     __syncthreads();
+    if (k0 + TK < k_dim) fetch(k0 + TK);
+    if (busy) {
+#pragma unroll
+      for (int kk = 0; kk < TK; ++kk) {
+        const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
+        const float4 b = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+        acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);
+        acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
+        acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]);
+        acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+      }
+    }
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -209,9 +259,13 @@ KVAD_EXPORT int kvad_grouped_linear(int dtype, int out_f32, const void* a, int64
   KVAD_REQUIRE(max_tiles >= 0 && n_out > 0 && k_dim > 0 && a && w && out && valid && tile_expert, "grouped_linear: bad arguments");
   if (max_tiles == 0) return KVAD_OK;
   dim3 grid((n_out + TN - 1) / TN, max_tiles), block(256);
+  // 16-byte pieces: K and the rows' stride in whole pieces, the bases on 16-byte boundaries
+  const int piece = dtype == KVAD_DTYPE_F32 ? 4 : 8;
+  const int vec = (k_dim % piece == 0 && ld_a % piece == 0 && expert_stride % piece == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) ? 1 : 0;
 #define KVAD_GL(T, TO)                                                                                                       \
   kvad_launch(grouped_linear_kernel<T, TO>, grid, block, 0, stream, (const T*)a, ld_a, in_rows, (const T*)w, expert_stride, (TO*)out, \
-              ld_out, out_rows, valid, tile_expert, n_out, k_dim)
+              ld_out, out_rows, valid, tile_expert, n_out, k_dim, vec)
   if (dtype == KVAD_DTYPE_F32) KVAD_GL(float, float);
   else if (dtype == KVAD_DTYPE_BF16 && out_f32) KVAD_GL(__nv_bfloat16, float);
   else if (dtype == KVAD_DTYPE_BF16) KVAD_GL(__nv_bfloat16, __nv_bfloat16);

@@ -24,7 +24,9 @@ import torch
 #: methods of `Ops` that launch kernels, and the argument whose leading size names the shape class
 _TIMED = {"embed": 4, "layernorm": 4, "linear": 3, "kv_store": 0, "attention": 0, "attention_prefill": 0, "attention_prompt": 0, "attention_decode_sums": 0,
           "attention_decode": 0, "argmax": 0, "sample": 0,
-          "rmsnorm": 3, "scale_add": 0, "rotary": 0, "gate_mul": 2, "kv_store_blend": 0, "latent_store": 0, "attention_scored": 0, "retention": 0, "linear_heads": 0}
+          "rmsnorm": 3, "scale_add": 0, "rotary": 0, "gate_mul": 2, "kv_store_blend": 0, "latent_store": 0, "attention_scored": 0, "retention": 0, "linear_heads": 0,
+          "gated_recurrence": 1, "short_conv": 0, "conv_state": 0, "head_norm_gate": 0, "moe_route": 0, "moe_sort": 0, "grouped_linear": 0,
+          "clamped_glu": 2, "moe_combine": 0}
 
 _records: list = []       # (label, start event, end event)
 _registered = False
@@ -41,6 +43,10 @@ def _label(name: str, args, kwargs) -> str:
         weight = args[1]
         epi = args[4] if len(args) > 4 else kwargs.get("epilogue", "store")
         return f"linear {rows}x{weight.shape[0]}x{weight.shape[1]} {epi}"
+    if name == "grouped_linear":
+        return f"grouped_linear rows={int(args[2].shape[0])} x{args[1].shape[1]}x{args[1].shape[2]}"
+    if name == "gated_recurrence":
+        return f"gated_recurrence {args[0]} rows={rows}"
     return f"{name} rows={rows}"
 
 
