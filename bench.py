@@ -211,6 +211,8 @@ def decode_bytes(engine, batch, mean_ctx):
         weights -= pos.table().numel() * elem
         weights += batch * pos.table().shape[1] * elem
     cache = batch * mean_ctx * engine.cache.layout.bytes_per_token(elem)
+    for t in engine.cache.state.values():               # fixed-size state: read and written once a step by every live request
+        cache += 2 * batch * t[:, 0].numel() * t.element_size()
     return weights + cache
 
 
@@ -308,10 +310,12 @@ def design_points(args, pk, pk_src):
                 if rep == 2:
                     profile.table()                     # (drops what the warm passes recorded)
                     profile.clear()
+                    profile.hold(True)                  # (the prompt pass's operations stay, whatever their row counts)
                 slots = [engine.open() for _ in prompts]
                 engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
                 for s in slots:
                     engine.close(s)
+            profile.hold(False)
             pr8 = random_prompts(args.batch, plen, vocab, 5)
             slots = [engine.open() for _ in pr8]
             engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, pr8)])

@@ -144,12 +144,15 @@ __device__ __forceinline__ void store_chunk(const float* v, void* out, int64_t l
 // One CTA per SM walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n fastest, then m, then the
 // K split): the ring of stages runs on from one tile into the next, and with two accumulators in tensor
 // memory the epilogue warps empty one while the MMAs fill the other.
+// Grouped (`tile_expert` given): W holds several matrices of `expert_rows` outputs each, one after another, and
+// tile_expert[m tile] says which of them the 128 rows of that tile multiply (negative: the tile is skipped).  The list
+// comes from the kernel before, so every role waits for it before its first tile.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS_WIDE, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, int tma_out,
                       const void* __restrict__ bias, int bias_f32, void* __restrict__ out, int64_t ldo,
-                      int M, int N, int K, int kb_per_split, int n_splits) {
+                      int M, int N, int K, int kb_per_split, int n_splits, const int* __restrict__ tile_expert, int expert_rows) {
   using T = Tile<BN>;
   constexpr int STAGES = T::STAGES, ACC_BUFS = T::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
@@ -174,12 +177,15 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int n_tiles = n_tiles_n * n_tiles_m * n_splits;
   const int kb_total = (K + BK - 1) / BK;
   // tile t: its corner and its share of K
-  auto tile_of = [&](int t, int* n0, int* m0, int* kb_begin, int* num_kb, int* z) {
+  // (w0: the tile's first row in W; negative: the tile is skipped)
+  auto tile_of = [&](int t, int* n0, int* m0, int* kb_begin, int* num_kb, int* z, int* w0) {
     const int nt = t % n_tiles_n, rest = t / n_tiles_n;
     const int mt = rest % n_tiles_m;
     *z = rest / n_tiles_m;
     *n0 = nt * BN;
     *m0 = mt * BM;
+    const int expert = tile_expert != nullptr ? tile_expert[mt] : 0;
+    *w0 = expert < 0 ? -1 : expert * expert_rows + *n0;
     *kb_begin = *z * kb_per_split;
     const int kb_end = *kb_begin + kb_per_split < kb_total ? *kb_begin + kb_per_split : kb_total;
     *num_kb = kb_end - *kb_begin;
@@ -202,21 +208,23 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (tile_expert != nullptr) pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;                       // stages filled so far, over all tiles
       bool waited = false, ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        int n0, m0, kb_begin, num_kb, z;
-        tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z);
+        int n0, m0, kb_begin, num_kb, z, w0;
+        tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z, &w0);
+        if (w0 < 0) continue;
         int i = 0;
         if (!waited) {
           // weights do not depend on the kernel before: the first tile's first stages are on the way before the wait
           const int pre = num_kb < STAGES ? num_kb : STAGES;
           for (int j = 0; j < pre; ++j) {
             mbar_expect_tx(&full_bar[j], T::A_BYTES + T::B_BYTES);
-            tma_load_2d(b_tiles + j * T::B_BYTES, &map_w, &full_bar[j], (kb_begin + j) * BK, n0);
+            tma_load_2d(b_tiles + j * T::B_BYTES, &map_w, &full_bar[j], (kb_begin + j) * BK, w0);
           }
           pdl_wait();
           waited = true;
@@ -230,7 +238,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           if (it >= (uint32_t)STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1)) { ok = false; break; }
           mbar_expect_tx(&full_bar[s], T::A_BYTES + T::B_BYTES);
           tma_load_2d(a_tiles + s * T::A_BYTES, &map_a, &full_bar[s], (kb_begin + i) * BK, m0);
-          tma_load_2d(b_tiles + s * T::B_BYTES, &map_w, &full_bar[s], (kb_begin + i) * BK, n0);
+          tma_load_2d(b_tiles + s * T::B_BYTES, &map_w, &full_bar[s], (kb_begin + i) * BK, w0);
         }
       }
     }
@@ -241,8 +249,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       int lt = 0;                            // tiles of this CTA so far
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-        int n0, m0, kb_begin, num_kb, z;
-        tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z);
+        int n0, m0, kb_begin, num_kb, z, w0;
+        tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z, &w0);
+        if (w0 < 0) {                        // (a skipped tile takes no accumulator)
+          --lt;
+          continue;
+        }
         const int buf = lt % ACC_BUFS;
         if (lt >= ACC_BUFS) {                // the epilogue has emptied this accumulator
           ok = mbar_wait(&tmem_empty_bar[buf], ((lt / ACC_BUFS) & 1) ^ 1);
@@ -273,8 +285,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     bool waited = false, slab_used = false, dead = false;
     int lt = 0;
     for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
-      int n0, m0, kb_begin, num_kb, z;
-      tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z);
+      int n0, m0, kb_begin, num_kb, z, w0;
+      tile_of(t, &n0, &m0, &kb_begin, &num_kb, &z, &w0);
+      if (w0 < 0) {
+        --lt;
+        continue;
+      }
       const int buf = lt % ACC_BUFS;
       const uint32_t acc = tmem_base + (uint32_t)(buf * T::TMEM_COLS) + ((uint32_t)(quarter * 32) << 16);
       const int row = m0 + quarter * 32 + lane;
@@ -846,7 +862,7 @@ int sm_count() {
 
 template <int BN, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int bias_f32, void* out, int64_t ldo,
-           int M, int N, int K, int splits, cudaStream_t stream) {
+           int M, int N, int K, int splits, cudaStream_t stream, const int* tile_expert = nullptr, int expert_rows = 0) {
   using T = Tile<BN>;
   // out by TMA where its rules hold: a 16-byte aligned base and row stride (not the 50257-wide logits)
   constexpr bool f32_out = (EPI == EPI_RESIDUAL || EPI == EPI_STORE_F32);
@@ -871,7 +887,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const void* bias, int b
   KVAD_REQUIRE(n_tiles < (1ll << 30), "linear_tcgen05: %lld tiles are more than one launch takes", (long long)n_tiles);
   const int ctas = n_tiles < sm_count() ? (int)n_tiles : sm_count();      // one CTA per SM walks the tiles
   kvad_launch(linear_tcgen05_kernel<BN, EPI>, dim3(ctas), dim3(NUM_THREADS_WIDE), T::SMEM, stream, ma, mw, mo, tma_out, bias,
-              bias_f32, out, ldo, M, N, K, kb_per_split, z);
+              bias_f32, out, ldo, M, N, K, kb_per_split, z, tile_expert, expert_rows);
   KVAD_CHECK_LAUNCH("linear_tcgen05");
   return KVAD_OK;
 }
@@ -1129,6 +1145,25 @@ KVAD_EXPORT int kvad_linear_tcgen05(const void* A, int64_t lda, const void* W, c
 
 // Tests: 1 keeps the swapped form on two-dimensional loads (one per K block) for every K; 2 takes the
 // grouped three-dimensional loads whenever K allows; 0 is the kernel's own choice (them, up to 16 rows).
+// out[p] = W[tile_expert[p / 128]] . A[p] for the rows p of every 128-row tile whose entry is not negative: W is
+// [experts x N, K] (the experts' matrices one after another), A [M, K] with M a multiple of 128, out [M, N] bfloat16 or,
+// with `out_f32`, float32.  No bias, K whole.
+KVAD_EXPORT int kvad_linear_tcgen05_grouped(const void* A, int64_t lda, const void* W, int n_experts, void* out, int64_t ldo,
+                                            const int* tile_expert, int M, int N, int K, int out_f32, cudaStream_t stream) {
+  KVAD_REQUIRE(M >= 0 && M % BM == 0 && N > 0 && K > 0 && n_experts > 0 && tile_expert != nullptr, "linear_tcgen05_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
+  if (K % 8 != 0 || lda % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "linear_tcgen05_grouped: K and the row stride must be multiples of 8, the operands on 16-byte boundaries");
+  KVAD_REQUIRE(lda >= K && ldo >= N && M / BM <= 65535, "linear_tcgen05_grouped: leading dimensions or row count out of range");
+  if (M == 0) return KVAD_OK;
+  CUtensorMap ma, mw;
+  int rc = tensor_map(A, lda, M, K, BM, &ma);
+  if (rc != KVAD_OK) return rc;
+  rc = tensor_map(W, K, n_experts * N, K, 128, &mw);
+  if (rc != KVAD_OK) return rc;
+  if (out_f32) return launch<128, EPI_STORE_F32>(ma, mw, nullptr, 0, out, ldo, M, N, K, 1, stream, tile_expert, N);
+  return launch<128, EPI_STORE>(ma, mw, nullptr, 0, out, ldo, M, N, K, 1, stream, tile_expert, N);
+}
+
 KVAD_EXPORT void kvad_linear_tcgen05_no_3d(int on) { g_no_3d = on == 1; g_force_3d = on == 2; }
 
 // Tests of the bounded waits: `wait_limit` > 0 sets how many polls a wait makes before it gives up (0: the

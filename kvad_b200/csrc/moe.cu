@@ -2,15 +2,18 @@
 //
 //   moe_route        z = router logits (32-bit) -> the `top` largest (ties: the lower index), weights = softmax over
 //                    the chosen logits only
-//   moe_sort         the (row, choice) slots grouped by expert, each expert's list padded to whole tiles of 32
-//                    positions; tile -> expert, position -> row and position -> slot (-1: padding)
+//   moe_sort         the (row, choice) slots grouped by expert, each expert's list padded to whole tiles of 32 (or 128)
+//                    positions; tile -> expert, position -> row, position -> slot (-1: padding) and slot -> position
+//   gather_rows      out[position] = a[row of the position] (zeros at padding): the operand of a product that reads
+//                    whole tiles by TMA
 //   grouped_linear   out[position] = W[expert of the position's tile] . a[row of the position]: a tiled product on
 //                    the CUDA cores (32-bit sums in k order, so a row's bits do not depend on its tile's company),
 //                    reading its rows and writing its outputs through the position lists
 //   clamped_glu      g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(alpha g) (u + 1)
-//   moe_combine      residual[row] += sum over the row's choices, in order, of weight * expert output
+//   moe_combine      residual[row] += sum over the row's choices, in order, of weight * expert output (found through
+//                    slot -> position)
 //
-// How many tiles a step can need depends only on its shape (rows x top / 32 + E at most), so the launches do not
+// How many tiles a step can need depends only on its shape (rows x top / tile + E at most), so the launches do not
 // depend on the routing and a step can be captured; tiles past the used ones leave at once.
 #include "common.cuh"
 
@@ -56,8 +59,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
 // One block.  counts -> padded offsets -> places.  Which place a slot gets inside its expert's list is not fixed
 // (shared-memory atomics); no result depends on it.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_experts, int max_tiles, int* __restrict__ tile_expert,
-                int* __restrict__ pos_row, int* __restrict__ pos_slot) {
+moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows,
+                int* __restrict__ tile_expert, int* __restrict__ pos_row, int* __restrict__ pos_slot, int* __restrict__ slot_pos) {
   extern __shared__ int sm[];
   int* counts = sm;
   int* offsets = sm + n_experts;
@@ -65,7 +68,7 @@ moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_expe
   pdl_launch_dependents();
   pdl_wait();
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = cursor[e] = 0;
-  for (int i = threadIdx.x; i < max_tiles * TM; i += blockDim.x) pos_row[i] = pos_slot[i] = -1;
+  for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) pos_row[i] = pos_slot[i] = -1;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
   __syncthreads();
   for (int i = threadIdx.x; i < n_slots; i += blockDim.x) atomicAdd(&counts[chosen[i]], 1);
@@ -73,8 +76,8 @@ moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_expe
   if (threadIdx.x == 0) {
     int tile = 0;
     for (int e = 0; e < n_experts; ++e) {
-      offsets[e] = tile * TM;
-      const int n = (counts[e] + TM - 1) / TM;
+      offsets[e] = tile * tile_rows;
+      const int n = (counts[e] + tile_rows - 1) / tile_rows;
       for (int t = 0; t < n; ++t) tile_expert[tile + t] = e;
       tile += n;
     }
@@ -85,6 +88,25 @@ moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_expe
     const int at = offsets[e] + atomicAdd(&cursor[e], 1);
     pos_row[at] = i / top;
     pos_slot[at] = i;
+    slot_pos[i] = at;
+  }
+}
+
+// A block per position; 16-byte pieces where `vec` says so.
+template <typename T>
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict__ pos_row, T* __restrict__ out, int64_t ld_out, int width,
+                   int vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x, r = pos_row[p];
+  T* o = out + (int64_t)p * ld_out;
+  if (vec) {
+    const int pieces = width * (int)sizeof(T) / 16;
+    const uint4* src = r >= 0 ? reinterpret_cast<const uint4*>(a + (int64_t)r * ld_a) : nullptr;
+    for (int i = threadIdx.x; i < pieces; i += 128) reinterpret_cast<uint4*>(o)[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+  } else {
+    for (int i = threadIdx.x; i < width; i += 128) o[i] = r >= 0 ? a[(int64_t)r * ld_a + i] : from_f32<T>(0.f);
   }
 }
 
@@ -209,15 +231,15 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate, int64_t ld_g, con
   }
 }
 
-__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ slots, const float* __restrict__ weight,
-                                   int n_rows, int width, int top) {
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ outs, int64_t ld_outs,
+                                   const int* __restrict__ slot_pos, const float* __restrict__ weight, int n_rows, int width, int top) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t total = (int64_t)n_rows * width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / width, c = i - r * width;
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(weight[r * top + k], slots[(r * top + k) * width + c], acc);
+    for (int k = 0; k < top; ++k) acc = fmaf(weight[r * top + k], outs[(int64_t)slot_pos[r * top + k] * ld_outs + c], acc);
     residual[i] += acc;
   }
 }
@@ -240,14 +262,14 @@ KVAD_EXPORT int kvad_moe_route(const float* logits, int64_t ld, int n_rows, int 
   return KVAD_OK;
 }
 
-KVAD_EXPORT int kvad_moe_sort(const int* chosen, int n_slots, int top, int n_experts, int max_tiles, int* tile_expert, int* pos_row,
-                              int* pos_slot, cudaStream_t stream) {
-  KVAD_REQUIRE(n_slots >= 0 && top > 0 && n_experts > 0 && n_experts <= 4096, "moe_sort: bad sizes");
-  KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / TM + n_experts, "moe_sort: %d tiles cannot hold %d slots of %d experts",
+KVAD_EXPORT int kvad_moe_sort(const int* chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows, int* tile_expert,
+                              int* pos_row, int* pos_slot, int* slot_pos, cudaStream_t stream) {
+  KVAD_REQUIRE(n_slots >= 0 && top > 0 && n_experts > 0 && n_experts <= 4096 && tile_rows > 0, "moe_sort: bad sizes");
+  KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / tile_rows + n_experts, "moe_sort: %d tiles cannot hold %d slots of %d experts",
                max_tiles, n_slots, n_experts);
   if (n_slots == 0) return KVAD_OK;
   kvad_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, chosen, n_slots, top, n_experts, max_tiles,
-              tile_expert, pos_row, pos_slot);
+              tile_rows, tile_expert, pos_row, pos_slot, slot_pos);
   KVAD_CHECK_LAUNCH("moe_sort");
   return KVAD_OK;
 }
@@ -292,12 +314,30 @@ KVAD_EXPORT int kvad_clamped_glu(int dtype, const void* gate, int64_t ld_g, cons
   return KVAD_OK;
 }
 
-KVAD_EXPORT int kvad_moe_combine(float* residual, const float* slots, const float* weight, int n_rows, int width, int top,
+KVAD_EXPORT int kvad_gather_rows(int dtype, const void* a, int64_t ld_a, const int* pos_row, void* out, int64_t ld_out, int n_pos, int width,
                                  cudaStream_t stream) {
-  KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && slots && weight, "moe_combine: bad arguments");
+  KVAD_REQUIRE(n_pos >= 0 && width > 0 && a && pos_row && out, "gather_rows: bad arguments");
+  if (n_pos == 0) return KVAD_OK;
+  const int es = dtype == KVAD_DTYPE_F32 ? 4 : 2;
+  const int vec = ((width * es) % 16 == 0 && (ld_a * es) % 16 == 0 && (ld_out * es) % 16 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) ? 1 : 0;
+  if (dtype == KVAD_DTYPE_F32)
+    kvad_launch(gather_rows_kernel<float>, dim3(n_pos), dim3(128), 0, stream, (const float*)a, ld_a, pos_row, (float*)out, ld_out, width, vec);
+  else if (dtype == KVAD_DTYPE_BF16)
+    kvad_launch(gather_rows_kernel<__nv_bfloat16>, dim3(n_pos), dim3(128), 0, stream, (const __nv_bfloat16*)a, ld_a, pos_row,
+                (__nv_bfloat16*)out, ld_out, width, vec);
+  else
+    KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "gather_rows: unknown dtype %d", dtype);
+  KVAD_CHECK_LAUNCH("gather_rows");
+  return KVAD_OK;
+}
+
+KVAD_EXPORT int kvad_moe_combine(float* residual, const float* outs, int64_t ld_outs, const int* slot_pos, const float* weight, int n_rows,
+                                 int width, int top, cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && outs && slot_pos && weight, "moe_combine: bad arguments");
   if (n_rows == 0) return KVAD_OK;
-  kvad_launch(moe_combine_kernel, dim3(flat_blocks((int64_t)n_rows * width, 256)), dim3(256), 0, stream, residual, slots, weight, n_rows,
-              width, top);
+  kvad_launch(moe_combine_kernel, dim3(flat_blocks((int64_t)n_rows * width, 256)), dim3(256), 0, stream, residual, outs, ld_outs, slot_pos,
+              weight, n_rows, width, top);
   KVAD_CHECK_LAUNCH("moe_combine");
   return KVAD_OK;
 }

@@ -54,6 +54,7 @@ _SIGNATURES = {
         "kvad_linear_tcgen05": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p],
         "kvad_linear_tcgen05_status": [],
+        "kvad_linear_tcgen05_grouped": [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "linear_rows": {
         "kvad_linear_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
@@ -121,11 +122,12 @@ _SIGNATURES = {
     "moe": {
         "kvad_moe_tile_rows": [],
         "kvad_moe_route": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "kvad_gather_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
         "kvad_grouped_linear": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_void_p],
         "kvad_clamped_glu": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_void_p],
-        "kvad_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "kvad_moe_combine": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "sampling": {
         "kvad_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -952,13 +954,21 @@ class Ops:
                                      ld_o, n, int(n_heads), dv, float(eps), _stream()), h)
 
     # -- routed feed-forward ------------------------------------------------------------------
-    def moe_tile_rows(self) -> int:
-        return int(lib("moe").kvad_moe_tile_rows())
+    MOE_WIDE_TILE = 128
+    MOE_WIDE_MIN_SLOTS = 512
 
-    def moe_max_tiles(self, n_rows: int, top: int, n_experts: int) -> int:
+    def moe_tile_rows(self, n_rows: int = 0, top: int = 1, pieces: bool = False) -> int:
+        """Positions a tile of the grouped products holds for a step of `n_rows` rows: 128 where the tensor-core form
+        runs (bfloat16, from 512 (row, choice) pairs on, `pieces`: both products' input sizes are whole 16-byte pieces),
+        else the CUDA-core form's 32.  Depends on the step's shape only."""
+        wide = (self.tensor_core_linear and n_rows * top >= self.MOE_WIDE_MIN_SLOTS and pieces)
+        return self.MOE_WIDE_TILE if wide else int(lib("moe").kvad_moe_tile_rows())
+
+    @staticmethod
+    def moe_max_tiles(n_rows: int, top: int, n_experts: int, tile_rows: int) -> int:
         """How many tiles of positions a step of this shape can need at most, whatever the routing."""
         slots = n_rows * top
-        return min(slots, slots // self.moe_tile_rows() + n_experts)
+        return min(slots, slots // tile_rows + n_experts)
 
     def moe_route(self, logits, top: int, chosen, weight) -> None:
         """Per row of float32 `logits` [rows, experts]: the `top` largest (ties: the lower index) into int32 `chosen`
@@ -971,32 +981,53 @@ class Ops:
         h = lib("moe")
         _check(h.kvad_moe_route(_ptr(logits), _rows_view(logits, "router logits"), n, E, int(top), _ptr(chosen), _ptr(weight), _stream()), h)
 
-    def moe_sort(self, chosen, n_experts: int, tile_expert, pos_row, pos_slot) -> None:
-        """Groups the (row, choice) slots of `chosen` [rows, top] by expert, every expert's list padded to whole tiles:
-        `tile_expert` [tiles] (-1: unused), `pos_row` / `pos_slot` [tiles x tile rows] (-1: padding)."""
-        _need_cuda(chosen, tile_expert, pos_row, pos_slot)
+    def moe_sort(self, chosen, n_experts: int, tile_rows: int, tile_expert, pos_row, pos_slot, slot_pos) -> None:
+        """Groups the (row, choice) slots of `chosen` [rows, top] by expert, every expert's list padded to whole tiles of
+        `tile_rows` positions: `tile_expert` [tiles] (-1: unused), `pos_row` / `pos_slot` [tiles x tile_rows] (-1: padding),
+        `slot_pos` [rows x top]: where each slot went."""
+        _need_cuda(chosen, tile_expert, pos_row, pos_slot, slot_pos)
         n, top = chosen.shape
         tiles = tile_expert.numel()
-        if any(t.dtype != torch.int32 or not t.is_contiguous() for t in (chosen, tile_expert, pos_row, pos_slot)) or \
-                pos_row.numel() < tiles * self.moe_tile_rows() or pos_slot.numel() < tiles * self.moe_tile_rows():
-            raise KernelError("moe_sort: int32 lists, a tile's rows per tile")
+        if any(t.dtype != torch.int32 or not t.is_contiguous() for t in (chosen, tile_expert, pos_row, pos_slot, slot_pos)) or \
+                pos_row.numel() < tiles * tile_rows or pos_slot.numel() < tiles * tile_rows or slot_pos.numel() < n * top:
+            raise KernelError("moe_sort: int32 lists, a tile's rows per tile, a place per slot")
         h = lib("moe")
-        _check(h.kvad_moe_sort(_ptr(chosen), n * top, top, int(n_experts), tiles, _ptr(tile_expert), _ptr(pos_row), _ptr(pos_slot), _stream()), h)
+        _check(h.kvad_moe_sort(_ptr(chosen), n * top, top, int(n_experts), tiles, int(tile_rows), _ptr(tile_expert), _ptr(pos_row), _ptr(pos_slot),
+                               _ptr(slot_pos), _stream()), h)
+
+    def gather_rows(self, a, pos_row, out) -> None:
+        """out[p] = a[pos_row[p]], zeros where pos_row[p] < 0."""
+        _need_cuda(a, pos_row, out)
+        ld_a, ld_o = _rows_view(a, "gather input"), _rows_view(out, "gather output")
+        if a.dtype != out.dtype or a.shape[1] != out.shape[1] or pos_row.dtype != torch.int32 or pos_row.numel() < out.shape[0]:
+            raise KernelError("gather_rows: rows of one dtype and width, an int32 row per output row")
+        h = lib("moe")
+        _check(h.kvad_gather_rows(_code(a.dtype), _ptr(a), ld_a, _ptr(pos_row), _ptr(out), ld_o, out.shape[0], out.shape[1], _stream()), h)
 
     def grouped_linear(self, a, weight, out, tile_expert, valid, *, in_rows=None, out_rows=None) -> None:
         """For every tile t of positions and position p in it: out[out_rows[p]] = weight[tile_expert[t]] . a[in_rows[p]]
         (`weight` [experts, outputs, inputs]; a row list that is None is the position itself; `valid[p]` < 0: padding).
-        `out` is of the compute dtype or float32."""
+        `out` is of the compute dtype or float32.  Tiles of 128 positions with no row lists run on the tensor cores
+        (whole tiles, padding included: the rows of `a` at padding must be finite), tiles of 32 on the CUDA cores."""
         _need_cuda(a, weight, out, tile_expert, valid, in_rows, out_rows)
         ld_a, ld_o = _rows_view(a, "grouped input"), _rows_view(out, "grouped output")
         if weight.dim() != 3 or not weight.is_contiguous() or a.dtype != self.dtype or weight.dtype != self.dtype or out.dtype not in (self.dtype, torch.float32):
             raise KernelError(f"grouped_linear: needs [experts, out, in] weights and rows of {self.dtype}")
-        _, n_out, k = weight.shape
+        E, n_out, k = weight.shape
         if a.shape[1] != k or out.shape[1] != n_out:
             raise KernelError("grouped_linear: rows do not match the experts' sizes")
+        tiles = tile_expert.numel()
+        tile_rows = valid.numel() // max(tiles, 1)
+        if tile_rows == self.MOE_WIDE_TILE:
+            if in_rows is not None or out_rows is not None or not self.tensor_core_linear or a.shape[0] != tiles * tile_rows or out.shape[0] != a.shape[0]:
+                raise KernelError("grouped_linear: tiles of 128 positions run on the tensor cores, rows in position order on both sides")
+            h = lib("linear_tcgen05")
+            _check(h.kvad_linear_tcgen05_grouped(_ptr(a), ld_a, _ptr(weight), E, _ptr(out), ld_o, _ptr(tile_expert), a.shape[0], n_out, k,
+                                                 1 if out.dtype == torch.float32 else 0, _stream()), h)
+            return
         h = lib("moe")
         _check(h.kvad_grouped_linear(self.code, 1 if out.dtype == torch.float32 else 0, _ptr(a), ld_a, _ptr(in_rows), _ptr(weight),
-                                     weight.stride(0), _ptr(out), ld_o, _ptr(out_rows), _ptr(valid), _ptr(tile_expert), tile_expert.numel(),
+                                     weight.stride(0), _ptr(out), ld_o, _ptr(out_rows), _ptr(valid), _ptr(tile_expert), tiles,
                                      n_out, k, _stream()), h)
 
     def clamped_glu(self, gate, up, out, limit: float, alpha: float = 1.702) -> None:
@@ -1009,16 +1040,17 @@ class Ops:
         _check(h.kvad_clamped_glu(self.code, _ptr(gate), ld_g, _ptr(up), ld_u, _ptr(out), ld_o, gate.shape[0], gate.shape[1], float(limit),
                                   float(alpha), _stream()), h)
 
-    def moe_combine(self, residual, slots, weight) -> None:
-        """residual[r] += sum_k weight[r, k] * slots[r * top + k], the choices in order (all float32)."""
-        _need_cuda(residual, slots, weight)
+    def moe_combine(self, residual, outs, slot_pos, weight) -> None:
+        """residual[r] += sum_k weight[r, k] * outs[slot_pos[r * top + k]], the choices in order (all float32)."""
+        _need_cuda(residual, outs, slot_pos, weight)
         n, width = residual.shape
         top = weight.shape[1]
-        if (any(t.dtype != torch.float32 or not t.is_contiguous() for t in (residual, slots, weight)) or weight.shape[0] != n
-                or slots.shape != (n * top, width)):
-            raise KernelError("moe_combine: float32 stream [rows, width], expert outputs [rows x top, width], weights [rows, top]")
+        if (any(t.dtype != torch.float32 for t in (residual, outs, weight)) or not residual.is_contiguous() or not weight.is_contiguous()
+                or weight.shape[0] != n or outs.shape[1] != width or slot_pos.dtype != torch.int32 or slot_pos.numel() < n * top):
+            raise KernelError("moe_combine: float32 stream [rows, width], expert outputs [positions, width], weights [rows, top], int32 places")
         h = lib("moe")
-        _check(h.kvad_moe_combine(_ptr(residual), _ptr(slots), _ptr(weight), n, width, top, _stream()), h)
+        _check(h.kvad_moe_combine(_ptr(residual), _ptr(outs), _rows_view(outs, "expert outputs"), _ptr(slot_pos), _ptr(weight), n, width, top,
+                                  _stream()), h)
 
     # -- sampling ------------------------------------------------------------------
     ARGMAX_CHUNK = 2048

@@ -91,17 +91,23 @@ class RoutedMLP(FeedForward):
         self.router.forward(ctx, h, logits, "store_f32")
         chosen, weight = ctx.buffer((n, top), torch.int32), ctx.buffer((n, top), torch.float32)
         ops.moe_route(logits, top, chosen, weight)
-        tiles, tm = ops.moe_max_tiles(n, top, E), ops.moe_tile_rows()
-        tile_expert = ctx.buffer((tiles,), torch.int32)
+        tm = ops.moe_tile_rows(n, top, self.width % 8 == 0 and ff % 8 == 0)
+        tiles = ops.moe_max_tiles(n, top, E, tm)
+        tile_expert, slot_pos = ctx.buffer((tiles,), torch.int32), ctx.buffer((n * top,), torch.int32)
         pos_row, pos_slot = ctx.buffer((tiles * tm,), torch.int32), ctx.buffer((tiles * tm,), torch.int32)
-        ops.moe_sort(chosen, E, tile_expert, pos_row, pos_slot)
+        ops.moe_sort(chosen, E, tm, tile_expert, pos_row, pos_slot, slot_pos)
         both = ctx.buffer((tiles * tm, 2 * ff))
-        ops.grouped_linear(h, self.w_in, both, tile_expert, pos_slot, in_rows=pos_row)
+        if tm == ops.MOE_WIDE_TILE:            # many rows: whole tiles on the tensor cores, from a copy of the rows in position order
+            rows = ctx.buffer((tiles * tm, self.width))
+            ops.gather_rows(h, pos_row, rows)
+            ops.grouped_linear(rows, self.w_in, both, tile_expert, pos_slot)
+        else:
+            ops.grouped_linear(h, self.w_in, both, tile_expert, pos_slot, in_rows=pos_row)
         hid = ctx.buffer((tiles * tm, ff))
         ops.clamped_glu(both[:, :ff], both[:, ff:], hid, self.limit, self.alpha)
-        outs = ctx.buffer((n * top, self.width), torch.float32)
-        ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot, out_rows=pos_slot)
-        ops.moe_combine(residual, outs, weight)
+        outs = ctx.buffer((tiles * tm, self.width), torch.float32)
+        ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot)
+        ops.moe_combine(residual, outs, slot_pos, weight)
         if self.shared is not None:
             self.shared.forward(ctx, h, residual)
 

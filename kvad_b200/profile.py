@@ -28,8 +28,15 @@ _TIMED = {"embed": 4, "layernorm": 4, "linear": 3, "kv_store": 0, "attention": 0
           "gated_recurrence": 1, "short_conv": 0, "conv_state": 0, "head_norm_gate": 0, "moe_route": 0, "moe_sort": 0, "grouped_linear": 0,
           "clamped_glu": 2, "moe_combine": 0}
 
-_records: list = []       # (label, start event, end event)
+_records: list = []       # (label, start event, end event, held)
 _registered = False
+_held = False             # records made while this is set outlive `clear(keep_rows=...)`
+
+
+def hold(on: bool) -> None:
+    """Records made from now on are kept (or no longer kept) by `clear(keep_rows=...)`, whatever their rows."""
+    global _held
+    _held = bool(on)
 
 
 def enabled() -> bool:
@@ -61,7 +68,7 @@ def instrument(ops) -> None:
             start.record()
             out = __fn(*args, **kwargs)
             end.record()
-            _records.append((_label(__name, args, kwargs), start, end))
+            _records.append((_label(__name, args, kwargs), start, end, _held))
             return out
 
         setattr(ops, name, functools.wraps(fn)(timed))
@@ -74,7 +81,7 @@ def table() -> list[tuple[str, int, float]]:
     """(label, calls, total microseconds), largest total first.  Waits for the device."""
     torch.cuda.synchronize()
     sums: dict[str, list] = {}
-    for label, start, end in _records:
+    for label, start, end, _ in _records:
         row = sums.setdefault(label, [0, 0.0])
         row[0] += 1
         row[1] += start.elapsed_time(end) * 1e3
@@ -95,9 +102,9 @@ def report(file=None) -> None:
 
 
 def clear(keep_rows=None) -> None:
-    """Forgets what has been recorded (`keep_rows`: but for operations of that many rows)."""
+    """Forgets what has been recorded (`keep_rows`: but for operations of that many rows and what was recorded under `hold`)."""
     torch.cuda.synchronize()
     if keep_rows is None:
         _records.clear()
     else:
-        _records[:] = [r for r in _records if f"rows={keep_rows}" in r[0] or f" {keep_rows}x" in r[0]]
+        _records[:] = [r for r in _records if r[3] or f"rows={keep_rows}" in r[0] or f" {keep_rows}x" in r[0]]

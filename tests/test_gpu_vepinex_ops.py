@@ -178,8 +178,11 @@ def test_router_choice_with_ties_and_weights_over_the_chosen_only(E, top):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n,E,top,width,ff", [(70, 5, 2, 24, 20), (3, 6, 3, 40, 33), (200, 3, 1, 18, 70), (33, 40, 4, 64, 16)])
+@pytest.mark.parametrize("n,E,top,width,ff", [(70, 5, 2, 24, 20), (3, 6, 3, 40, 33), (200, 3, 1, 18, 70), (33, 40, 4, 64, 16), (300, 6, 2, 72, 200),
+                                              (700, 3, 1, 136, 24)])
 def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
+    """Small steps run tiles of 32 positions on the CUDA cores; from 512 (row, choice) pairs on, bfloat16 with sizes in
+    16-byte pieces runs tiles of 128 on the tensor cores from a gathered copy of the rows."""
     rng, ops, limit = np.random.default_rng(n), Ops(DT[dtype]), 0.8
     h = stored(rng.standard_normal((n, width)), dtype)
     w_in = stored(rng.standard_normal((E, 2 * ff, width)) / np.sqrt(width) * 2, dtype)
@@ -188,23 +191,31 @@ def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
     z[:, E - 1] = -50.0               # an expert that nobody chooses
     chosen_ref, weight_ref = pl.choose(stored(z, "float32"), top)
     chosen, weight = i32(chosen_ref), dev(weight_ref, torch.float32)
-    tiles, tm = ops.moe_max_tiles(n, top, E), ops.moe_tile_rows()
+    tm = ops.moe_tile_rows(n, top, width % 8 == 0 and ff % 8 == 0)
+    assert tm == (128 if dtype == "bfloat16" and n * top >= 512 and width % 8 == 0 and ff % 8 == 0 else 32)
+    tiles = ops.moe_max_tiles(n, top, E, tm)
     tile_expert = torch.full((tiles,), -9, device="cuda", dtype=torch.int32)
     pos_row, pos_slot = (torch.full((tiles * tm,), -9, device="cuda", dtype=torch.int32) for _ in range(2))
-    ops.moe_sort(chosen, E, tile_expert, pos_row, pos_slot)
-    te, pr, ps = tile_expert.cpu().numpy(), pos_row.cpu().numpy(), pos_slot.cpu().numpy()
+    slot_pos = torch.full((n * top,), -9, device="cuda", dtype=torch.int32)
+    ops.moe_sort(chosen, E, tm, tile_expert, pos_row, pos_slot, slot_pos)
+    te, pr, ps, sp = tile_expert.cpu().numpy(), pos_row.cpu().numpy(), pos_slot.cpu().numpy(), slot_pos.cpu().numpy()
     assert sorted(ps[ps >= 0].tolist()) == list(range(n * top))                             # every slot once
     for p in np.nonzero(ps >= 0)[0]:
-        assert te[p // tm] == chosen_ref.reshape(-1)[ps[p]] and pr[p] == ps[p] // top       # in a tile of its expert
+        assert te[p // tm] == chosen_ref.reshape(-1)[ps[p]] and pr[p] == ps[p] // top and sp[ps[p]] == p      # in a tile of its expert
     both = torch.full((tiles * tm, 2 * ff), float("nan"), device="cuda", dtype=DT[dtype])
-    ops.grouped_linear(dev(h, DT[dtype]), dev(w_in, DT[dtype]), both, tile_expert, pos_slot, in_rows=pos_row)
+    if tm == 128:
+        rows = torch.full((tiles * tm, width), float("nan"), device="cuda", dtype=DT[dtype])
+        ops.gather_rows(dev(h, DT[dtype]), pos_row, rows)
+        ops.grouped_linear(rows, dev(w_in, DT[dtype]), both, tile_expert, pos_slot)
+    else:
+        ops.grouped_linear(dev(h, DT[dtype]), dev(w_in, DT[dtype]), both, tile_expert, pos_slot, in_rows=pos_row)
     hid = torch.empty((tiles * tm, ff), device="cuda", dtype=DT[dtype])
     ops.clamped_glu(both[:, :ff], both[:, ff:], hid, limit)
-    outs = torch.full((n * top, width), float("nan"), device="cuda")
-    ops.grouped_linear(hid, dev(w_out, DT[dtype]), outs, tile_expert, pos_slot, out_rows=pos_slot)
+    outs = torch.full((tiles * tm, width), float("nan"), device="cuda")
+    ops.grouped_linear(hid, dev(w_out, DT[dtype]), outs, tile_expert, pos_slot)
     residual = stored(rng.standard_normal((n, width)), "float32")
     res = dev(residual, torch.float32)
-    ops.moe_combine(res, outs, weight)
+    ops.moe_combine(res, outs, slot_pos, weight)
     want = residual.copy()
     for r in range(n):
         for e, g in zip(chosen_ref[r], weight_ref[r]):
@@ -213,6 +224,9 @@ def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
                 y = stored(y, dtype)
             want[r] += g * (y @ w_out[e].T)
     assert rel(res, want) < (1e-5 if dtype == "float32" else 1e-2)
+    if tm == 128:
+        from kvad_b200.ops import tcgen05_wait_timeouts
+        assert tcgen05_wait_timeouts() == 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
