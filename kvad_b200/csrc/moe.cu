@@ -116,6 +116,7 @@ gather_rows_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict_
 // rows a step (decoding) most of a tile is padding and the kernel is a stream of the chosen experts' weights.
 template <typename T, int N> struct Piece;
 template <> struct Piece<float, 4> { using type = float4; };
+template <> struct Piece<float, 8> { using type = float4; };
 template <> struct Piece<__nv_bfloat16, 4> { using type = uint2; };
 template <> struct Piece<__nv_bfloat16, 8> { using type = uint4; };
 
@@ -217,6 +218,73 @@ grouped_linear_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restri
   }
 }
 
+// The same product for steps of a few rows (decoding): a stream of the chosen experts' weights.  A warp owns two outputs
+// of one tile; its lanes take every 32nd 16-byte piece of the two weight rows (several on their way at once) and
+// multiply them with the same pieces of up to eight of the tile's rows (which stay in the L1); a shuffle tree per
+// (row, output) at the end.  A tile with more than eight rows streams its weights again per eight, from the L2.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+grouped_rows_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict__ in_rows, const T* __restrict__ w,
+                    int64_t expert_stride, TO* __restrict__ out, int64_t ld_out, const int* __restrict__ out_rows,
+                    const int* __restrict__ valid, const int* __restrict__ tile_expert, int n_out, int k_dim) {
+  constexpr int R = 8, CU = 2, PIECE = 16 / (int)sizeof(T);
+  __shared__ int rows_in[TM], rows_out[TM], n_valid;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.y, expert = tile_expert[tile];
+  if (expert < 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < TM) {                               // the tile's used positions, side by side
+    const int p = tile * TM + tid;
+    const bool used = valid[p] >= 0;
+    const unsigned mask = __ballot_sync(0xffffffffu, used);
+    if (used) {
+      const int at = __popc(mask & ((1u << tid) - 1u));
+      rows_in[at] = in_rows ? in_rows[p] : p;
+      rows_out[at] = out_rows ? out_rows[p] : p;
+    }
+    if (tid == 0) n_valid = __popc(mask);
+  }
+  __syncthreads();
+  const int col0 = (blockIdx.x * 8 + warp) * CU;
+  if (col0 >= n_out) return;
+  const T* we = w + (int64_t)expert * expert_stride;
+  const T* w0 = we + (int64_t)col0 * k_dim;
+  const T* w1 = we + (int64_t)(col0 + 1 < n_out ? col0 + 1 : col0) * k_dim;
+  for (int r0 = 0; r0 < n_valid; r0 += R) {
+    const int nr = min(R, n_valid - r0);
+    float acc[R][CU] = {};
+#pragma unroll 4
+    for (int k = lane * PIECE; k < k_dim; k += 32 * PIECE) {
+      float wa[PIECE], wb[PIECE], av[PIECE];
+      load_piece<T, PIECE>(w0 + k, PIECE, true, wa);
+      load_piece<T, PIECE>(w1 + k, PIECE, true, wb);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (r < nr) {
+          load_piece<T, PIECE>(a + (int64_t)rows_in[r0 + r] * ld_a + k, PIECE, true, av);
+#pragma unroll
+          for (int j = 0; j < PIECE; ++j) {
+            acc[r][0] = fmaf(av[j], wa[j], acc[r][0]);
+            acc[r][1] = fmaf(av[j], wb[j], acc[r][1]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r < nr) {
+        const float s0 = warp_sum(acc[r][0]), s1 = warp_sum(acc[r][1]);
+        if (lane == 0) {
+          TO* o = out + (int64_t)rows_out[r0 + r] * ld_out + col0;
+          o[0] = from_f32<TO>(s0);
+          if (col0 + 1 < n_out) o[1] = from_f32<TO>(s1);
+        }
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gate, int64_t ld_g, const T* __restrict__ up, int64_t ld_u, T* __restrict__ out,
                                    int64_t ld_o, int n_rows, int width, float limit, float alpha) {
@@ -275,9 +343,11 @@ KVAD_EXPORT int kvad_moe_sort(const int* chosen, int n_slots, int top, int n_exp
 }
 
 // Position p reads row in_rows[p] of `a` (null: row p) and writes row out_rows[p] of `out` (null: row p); valid[p] < 0: padding.
+// few_rows: the step has so few rows that most of a tile is padding; where the sizes allow 16-byte pieces the weight-streaming
+// form runs.
 KVAD_EXPORT int kvad_grouped_linear(int dtype, int out_f32, const void* a, int64_t ld_a, const int* in_rows, const void* w,
                                     int64_t expert_stride, void* out, int64_t ld_out, const int* out_rows, const int* valid,
-                                    const int* tile_expert, int max_tiles, int n_out, int k_dim, cudaStream_t stream) {
+                                    const int* tile_expert, int max_tiles, int n_out, int k_dim, int few_rows, cudaStream_t stream) {
   KVAD_REQUIRE(max_tiles >= 0 && n_out > 0 && k_dim > 0 && a && w && out && valid && tile_expert, "grouped_linear: bad arguments");
   if (max_tiles == 0) return KVAD_OK;
   dim3 grid((n_out + TN - 1) / TN, max_tiles), block(256);
@@ -285,6 +355,19 @@ KVAD_EXPORT int kvad_grouped_linear(int dtype, int out_f32, const void* a, int64
   const int piece = dtype == KVAD_DTYPE_F32 ? 4 : 8;
   const int vec = (k_dim % piece == 0 && ld_a % piece == 0 && expert_stride % piece == 0 &&
                    ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) ? 1 : 0;
+  if (few_rows && vec) {
+    dim3 rgrid((n_out + 15) / 16, max_tiles);
+#define KVAD_GR(T, TO)                                                                                                     \
+  kvad_launch(grouped_rows_kernel<T, TO>, rgrid, block, 0, stream, (const T*)a, ld_a, in_rows, (const T*)w, expert_stride, (TO*)out, \
+              ld_out, out_rows, valid, tile_expert, n_out, k_dim)
+    if (dtype == KVAD_DTYPE_F32) KVAD_GR(float, float);
+    else if (dtype == KVAD_DTYPE_BF16 && out_f32) KVAD_GR(__nv_bfloat16, float);
+    else if (dtype == KVAD_DTYPE_BF16) KVAD_GR(__nv_bfloat16, __nv_bfloat16);
+    else KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "grouped_linear: unknown dtype %d", dtype);
+#undef KVAD_GR
+    KVAD_CHECK_LAUNCH("grouped_linear");
+    return KVAD_OK;
+  }
 #define KVAD_GL(T, TO)                                                                                                       \
   kvad_launch(grouped_linear_kernel<T, TO>, grid, block, 0, stream, (const T*)a, ld_a, in_rows, (const T*)w, expert_stride, (TO*)out, \
               ld_out, out_rows, valid, tile_expert, n_out, k_dim, vec)

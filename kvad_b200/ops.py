@@ -125,7 +125,7 @@ _SIGNATURES = {
         "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "kvad_gather_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
         "kvad_grouped_linear": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                                c_int, c_int, c_int, c_void_p],
+                                c_int, c_int, c_int, c_int, c_void_p],
         "kvad_clamped_glu": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_void_p],
         "kvad_moe_combine": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
@@ -1004,11 +1004,15 @@ class Ops:
         h = lib("moe")
         _check(h.kvad_gather_rows(_code(a.dtype), _ptr(a), ld_a, _ptr(pos_row), _ptr(out), ld_o, out.shape[0], out.shape[1], _stream()), h)
 
-    def grouped_linear(self, a, weight, out, tile_expert, valid, *, in_rows=None, out_rows=None) -> None:
+    MOE_FEW_SLOTS = 128
+
+    def grouped_linear(self, a, weight, out, tile_expert, valid, *, in_rows=None, out_rows=None, few_rows: bool = False) -> None:
         """For every tile t of positions and position p in it: out[out_rows[p]] = weight[tile_expert[t]] . a[in_rows[p]]
         (`weight` [experts, outputs, inputs]; a row list that is None is the position itself; `valid[p]` < 0: padding).
         `out` is of the compute dtype or float32.  Tiles of 128 positions with no row lists run on the tensor cores
-        (whole tiles, padding included: the rows of `a` at padding must be finite), tiles of 32 on the CUDA cores."""
+        (whole tiles, padding included: the rows of `a` at padding must be finite), tiles of 32 on the CUDA cores: as tiled
+        products, or with `few_rows` (a step of at most `MOE_FEW_SLOTS` (row, choice) pairs: most of a tile is padding) as a
+        stream of the chosen experts' weights."""
         _need_cuda(a, weight, out, tile_expert, valid, in_rows, out_rows)
         ld_a, ld_o = _rows_view(a, "grouped input"), _rows_view(out, "grouped output")
         if weight.dim() != 3 or not weight.is_contiguous() or a.dtype != self.dtype or weight.dtype != self.dtype or out.dtype not in (self.dtype, torch.float32):
@@ -1028,7 +1032,7 @@ class Ops:
         h = lib("moe")
         _check(h.kvad_grouped_linear(self.code, 1 if out.dtype == torch.float32 else 0, _ptr(a), ld_a, _ptr(in_rows), _ptr(weight),
                                      weight.stride(0), _ptr(out), ld_o, _ptr(out_rows), _ptr(valid), _ptr(tile_expert), tiles,
-                                     n_out, k, _stream()), h)
+                                     n_out, k, int(bool(few_rows)), _stream()), h)
 
     def clamped_glu(self, gate, up, out, limit: float, alpha: float = 1.702) -> None:
         """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), 32-bit arithmetic."""

@@ -97,16 +97,17 @@ class RoutedMLP(FeedForward):
         pos_row, pos_slot = ctx.buffer((tiles * tm,), torch.int32), ctx.buffer((tiles * tm,), torch.int32)
         ops.moe_sort(chosen, E, tm, tile_expert, pos_row, pos_slot, slot_pos)
         both = ctx.buffer((tiles * tm, 2 * ff))
+        few = n * top <= ops.MOE_FEW_SLOTS      # (by the step's shape only)
         if tm == ops.MOE_WIDE_TILE:            # many rows: whole tiles on the tensor cores, from a copy of the rows in position order
             rows = ctx.buffer((tiles * tm, self.width))
             ops.gather_rows(h, pos_row, rows)
             ops.grouped_linear(rows, self.w_in, both, tile_expert, pos_slot)
         else:
-            ops.grouped_linear(h, self.w_in, both, tile_expert, pos_slot, in_rows=pos_row)
+            ops.grouped_linear(h, self.w_in, both, tile_expert, pos_slot, in_rows=pos_row, few_rows=few)
         hid = ctx.buffer((tiles * tm, ff))
         ops.clamped_glu(both[:, :ff], both[:, ff:], hid, self.limit, self.alpha)
         outs = ctx.buffer((tiles * tm, self.width), torch.float32)
-        ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot)
+        ops.grouped_linear(hid, self.w_out, outs, tile_expert, pos_slot, few_rows=few)
         ops.moe_combine(residual, outs, slot_pos, weight)
         if self.shared is not None:
             self.shared.forward(ctx, h, residual)

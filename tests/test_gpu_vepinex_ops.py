@@ -179,11 +179,13 @@ def test_router_choice_with_ties_and_weights_over_the_chosen_only(E, top):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n,E,top,width,ff", [(70, 5, 2, 24, 20), (3, 6, 3, 40, 33), (200, 3, 1, 18, 70), (33, 40, 4, 64, 16), (300, 6, 2, 72, 200),
-                                              (700, 3, 1, 136, 24)])
+                                              (700, 3, 1, 136, 24), (3, 6, 3, 40, 32), (40, 2, 2, 264, 16), (1, 4, 2, 520, 24)])
 def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
     """Small steps run tiles of 32 positions on the CUDA cores; from 512 (row, choice) pairs on, bfloat16 with sizes in
     16-byte pieces runs tiles of 128 on the tensor cores from a gathered copy of the rows."""
+    from kvad_b200.ops import tcgen05_wait_timeouts
     rng, ops, limit = np.random.default_rng(n), Ops(DT[dtype]), 0.8
+    timeouts_before = tcgen05_wait_timeouts() if dtype == "bfloat16" else 0
     h = stored(rng.standard_normal((n, width)), dtype)
     w_in = stored(rng.standard_normal((E, 2 * ff, width)) / np.sqrt(width) * 2, dtype)
     w_out = stored(rng.standard_normal((E, width, ff)) / np.sqrt(ff), dtype)
@@ -191,6 +193,7 @@ def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
     z[:, E - 1] = -50.0               # an expert that nobody chooses
     chosen_ref, weight_ref = pl.choose(stored(z, "float32"), top)
     chosen, weight = i32(chosen_ref), dev(weight_ref, torch.float32)
+    few = n * top <= ops.MOE_FEW_SLOTS          # (the weight-streaming form, where the sizes allow 16-byte pieces)
     tm = ops.moe_tile_rows(n, top, width % 8 == 0 and ff % 8 == 0)
     assert tm == (128 if dtype == "bfloat16" and n * top >= 512 and width % 8 == 0 and ff % 8 == 0 else 32)
     tiles = ops.moe_max_tiles(n, top, E, tm)
@@ -208,11 +211,11 @@ def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
         ops.gather_rows(dev(h, DT[dtype]), pos_row, rows)
         ops.grouped_linear(rows, dev(w_in, DT[dtype]), both, tile_expert, pos_slot)
     else:
-        ops.grouped_linear(dev(h, DT[dtype]), dev(w_in, DT[dtype]), both, tile_expert, pos_slot, in_rows=pos_row)
+        ops.grouped_linear(dev(h, DT[dtype]), dev(w_in, DT[dtype]), both, tile_expert, pos_slot, in_rows=pos_row, few_rows=few)
     hid = torch.empty((tiles * tm, ff), device="cuda", dtype=DT[dtype])
     ops.clamped_glu(both[:, :ff], both[:, ff:], hid, limit)
     outs = torch.full((tiles * tm, width), float("nan"), device="cuda")
-    ops.grouped_linear(hid, dev(w_out, DT[dtype]), outs, tile_expert, pos_slot)
+    ops.grouped_linear(hid, dev(w_out, DT[dtype]), outs, tile_expert, pos_slot, few_rows=few)
     residual = stored(rng.standard_normal((n, width)), "float32")
     res = dev(residual, torch.float32)
     ops.moe_combine(res, outs, slot_pos, weight)
@@ -225,8 +228,7 @@ def test_routed_experts_against_each_row_by_itself(dtype, n, E, top, width, ff):
             want[r] += g * (y @ w_out[e].T)
     assert rel(res, want) < (1e-5 if dtype == "float32" else 1e-2)
     if tm == 128:
-        from kvad_b200.ops import tcgen05_wait_timeouts
-        assert tcgen05_wait_timeouts() == 0
+        assert tcgen05_wait_timeouts() == timeouts_before            # no bounded wait of the tensor-core product ran out
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
