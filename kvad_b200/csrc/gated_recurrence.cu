@@ -220,22 +220,27 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   }
 }
 
-// A block per row.  x: this step's projections; inputs before the step's first row come from the sequence's kept
-// inputs [taps - 1, channels] (position p0 - taps + 1 + i at row i), inputs before position 0 are zero.
+// A block per (row, chunk of columns); a chunk holds whole unit heads.  x: this step's projections; inputs before the
+// step's first row come from the sequence's kept inputs [taps - 1, channels] (position p0 - taps + 1 + i at row i), inputs
+// before position 0 are zero.  Four columns of a thread are on their way at once: with a few rows a step the kernel is a
+// chain of trips to memory and nothing else.
 template <typename T>
 __global__ void __launch_bounds__(128)
 short_conv_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict__ taps, float* __restrict__ y, int64_t ld_y,
                   const float* __restrict__ state, int64_t state_stride, int64_t conv_off, const int* __restrict__ row_seq,
                   const int* __restrict__ row_pos, const int* __restrict__ seq_starts, const int* __restrict__ seq_slots,
                   int channels, int n_taps, int n_sigmoid, int unit_heads, int unit_dim, int scaled_heads, float head_scale,
-                  float unit_eps) {
+                  float unit_eps, int chunk) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x, s = row_seq[r], pos = row_pos[r], first = seq_starts[s];
   const int p0 = pos - (r - first);
   const float* kept = state + (int64_t)seq_slots[s] * state_stride + conv_off;
   float* yr = y + (int64_t)r * ld_y;
-  for (int c = threadIdx.x; c < channels; c += 128) {
+  const int lo = blockIdx.y * chunk, hi = min(lo + chunk, channels + n_sigmoid);
+  const int conv_hi = min(hi, channels);
+#pragma unroll 4
+  for (int c = lo + threadIdx.x; c < conv_hi; c += 128) {
     float acc = 0.f;
     for (int j = 0; j < n_taps; ++j) {
       const int pp = pos - (n_taps - 1) + j;
@@ -246,11 +251,12 @@ short_conv_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict__ t
     }
     yr[c] = silu_f(acc);
   }
-  for (int c = channels + threadIdx.x; c < channels + n_sigmoid; c += 128) yr[c] = sigmoid_f(to_f32(x[(int64_t)r * ld_x + c]));
-  if (unit_heads > 0) {
+  for (int c = max(lo, channels) + threadIdx.x; c < hi; c += 128) yr[c] = sigmoid_f(to_f32(x[(int64_t)r * ld_x + c]));
+  if (unit_heads > 0 && lo < unit_heads * unit_dim) {
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int hd = warp; hd < unit_heads; hd += 4) {
+    const int hd_hi = min(unit_heads, hi / unit_dim);
+    for (int hd = lo / unit_dim + warp; hd < hd_hi; hd += 4) {
       float* hp = yr + (int64_t)hd * unit_dim;
       float sq = 0.f;
       for (int d = lane; d < unit_dim; d += 32) sq = fmaf(hp[d], hp[d], sq);
@@ -365,14 +371,19 @@ KVAD_EXPORT int kvad_short_conv(int dtype, const void* x, int64_t ld_x, const vo
   KVAD_REQUIRE(n_rows >= 0 && channels > 0 && n_taps >= 1 && n_taps <= 16 && n_sigmoid >= 0, "short_conv: bad sizes");
   KVAD_REQUIRE(unit_heads >= 0 && (int64_t)unit_heads * unit_dim <= channels && scaled_heads <= unit_heads, "short_conv: the unit heads do not fit the channels");
   if (n_rows == 0) return KVAD_OK;
-  dim3 grid(n_rows), block(128);
+  // columns in chunks of at least 512 that hold whole unit heads (one chunk where the heads do not allow it)
+  const int total = channels + n_sigmoid;
+  int chunk = total;
+  if (unit_heads == 0) chunk = 512;
+  else if (unit_dim <= 4096) chunk = (512 + unit_dim - 1) / unit_dim * unit_dim;
+  dim3 grid(n_rows, (total + chunk - 1) / chunk), block(128);
   if (dtype == KVAD_DTYPE_F32)
     kvad_launch(short_conv_kernel<float>, grid, block, 0, stream, (const float*)x, ld_x, (const float*)taps, y, ld_y, state, state_stride,
-                conv_off, row_seq, row_pos, seq_starts, seq_slots, channels, n_taps, n_sigmoid, unit_heads, unit_dim, scaled_heads, head_scale, unit_eps);
+                conv_off, row_seq, row_pos, seq_starts, seq_slots, channels, n_taps, n_sigmoid, unit_heads, unit_dim, scaled_heads, head_scale, unit_eps, chunk);
   else if (dtype == KVAD_DTYPE_BF16)
     kvad_launch(short_conv_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ld_x, (const __nv_bfloat16*)taps, y, ld_y,
                 state, state_stride, conv_off, row_seq, row_pos, seq_starts, seq_slots, channels, n_taps, n_sigmoid, unit_heads, unit_dim,
-                scaled_heads, head_scale, unit_eps);
+                scaled_heads, head_scale, unit_eps, chunk);
   else
     KVAD_FAIL(KVAD_ERR_UNSUPPORTED, "short_conv: unknown dtype %d", dtype);
   KVAD_CHECK_LAUNCH("short_conv");

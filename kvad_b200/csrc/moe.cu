@@ -23,12 +23,8 @@ namespace {
 
 constexpr int TM = 32, TN = 64, TK = 32;
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n_rows, int n_experts, int top,
-                                 int* __restrict__ chosen, float* __restrict__ weight) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= n_rows) return;
+__device__ __forceinline__ void route_row(const float* __restrict__ logits, int64_t ld, int r, int n_experts, int top,
+                                          int* __restrict__ chosen, float* __restrict__ weight) {
   const float* z = logits + (int64_t)r * ld;
   int* mine = chosen + (int64_t)r * top;
   float* wt = weight + (int64_t)r * top;
@@ -56,11 +52,20 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
   for (int k = 0; k < top; ++k) wt[k] /= sum;
 }
 
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n_rows, int n_experts, int top,
+                                 int* __restrict__ chosen, float* __restrict__ weight) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < n_rows) route_row(logits, ld, r, n_experts, top, chosen, weight);
+}
+
 // One block.  counts -> padded offsets -> places.  Which place a slot gets inside its expert's list is not fixed
 // (shared-memory atomics); no result depends on it.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows,
-                int* __restrict__ tile_expert, int* __restrict__ pos_row, int* __restrict__ pos_slot, int* __restrict__ slot_pos) {
+moe_sort_kernel(int* __restrict__ chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows,
+                int* __restrict__ tile_expert, int* __restrict__ pos_row, int* __restrict__ pos_slot, int* __restrict__ slot_pos,
+                const float* __restrict__ logits, int64_t ld_logits, float* __restrict__ weight) {
   extern __shared__ int sm[];
   int* counts = sm;
   int* offsets = sm + n_experts;
@@ -70,6 +75,8 @@ moe_sort_kernel(const int* __restrict__ chosen, int n_slots, int top, int n_expe
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = cursor[e] = 0;
   for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) pos_row[i] = pos_slot[i] = -1;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+  if (logits != nullptr)                       // the routing itself first, a thread per row: one launch instead of two
+    for (int r = threadIdx.x; r < n_slots / top; r += blockDim.x) route_row(logits, ld_logits, r, n_experts, top, chosen, weight);
   __syncthreads();
   for (int i = threadIdx.x; i < n_slots; i += blockDim.x) atomicAdd(&counts[chosen[i]], 1);
   __syncthreads();
@@ -330,14 +337,17 @@ KVAD_EXPORT int kvad_moe_route(const float* logits, int64_t ld, int n_rows, int 
   return KVAD_OK;
 }
 
-KVAD_EXPORT int kvad_moe_sort(const int* chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows, int* tile_expert,
-                              int* pos_row, int* pos_slot, int* slot_pos, cudaStream_t stream) {
+// logits given: the rows are routed first (`chosen` and `weight` are written), then grouped.
+KVAD_EXPORT int kvad_moe_sort(int* chosen, int n_slots, int top, int n_experts, int max_tiles, int tile_rows, int* tile_expert,
+                              int* pos_row, int* pos_slot, int* slot_pos, const float* logits, int64_t ld_logits, float* weight,
+                              cudaStream_t stream) {
   KVAD_REQUIRE(n_slots >= 0 && top > 0 && n_experts > 0 && n_experts <= 4096 && tile_rows > 0, "moe_sort: bad sizes");
+  KVAD_REQUIRE(logits == nullptr || (weight != nullptr && top <= n_experts && ld_logits >= n_experts), "moe_sort: routing needs weights to write");
   KVAD_REQUIRE(max_tiles >= n_slots || max_tiles >= n_slots / tile_rows + n_experts, "moe_sort: %d tiles cannot hold %d slots of %d experts",
                max_tiles, n_slots, n_experts);
   if (n_slots == 0) return KVAD_OK;
   kvad_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, chosen, n_slots, top, n_experts, max_tiles,
-              tile_rows, tile_expert, pos_row, pos_slot, slot_pos);
+              tile_rows, tile_expert, pos_row, pos_slot, slot_pos, logits, ld_logits, weight);
   KVAD_CHECK_LAUNCH("moe_sort");
   return KVAD_OK;
 }

@@ -122,7 +122,7 @@ _SIGNATURES = {
     "moe": {
         "kvad_moe_tile_rows": [],
         "kvad_moe_route": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "kvad_moe_sort": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
         "kvad_gather_rows": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
         "kvad_grouped_linear": [c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_void_p],
@@ -981,11 +981,18 @@ class Ops:
         h = lib("moe")
         _check(h.kvad_moe_route(_ptr(logits), _rows_view(logits, "router logits"), n, E, int(top), _ptr(chosen), _ptr(weight), _stream()), h)
 
-    def moe_sort(self, chosen, n_experts: int, tile_rows: int, tile_expert, pos_row, pos_slot, slot_pos) -> None:
+    def moe_sort(self, chosen, n_experts: int, tile_rows: int, tile_expert, pos_row, pos_slot, slot_pos, *, logits=None, weight=None) -> None:
         """Groups the (row, choice) slots of `chosen` [rows, top] by expert, every expert's list padded to whole tiles of
         `tile_rows` positions: `tile_expert` [tiles] (-1: unused), `pos_row` / `pos_slot` [tiles x tile_rows] (-1: padding),
-        `slot_pos` [rows x top]: where each slot went."""
-        _need_cuda(chosen, tile_expert, pos_row, pos_slot, slot_pos)
+        `slot_pos` [rows x top]: where each slot went.  With `logits` and `weight` the same launch routes the rows first
+        (as `moe_route` does) and writes `chosen` and `weight`."""
+        _need_cuda(chosen, tile_expert, pos_row, pos_slot, slot_pos, logits, weight)
+        ld_z = 0
+        if logits is not None:
+            ld_z = _rows_view(logits, "router logits")
+            if (logits.dtype != torch.float32 or logits.shape != (chosen.shape[0], n_experts) or weight is None or weight.dtype != torch.float32
+                    or weight.shape != chosen.shape or not weight.is_contiguous()):
+                raise KernelError("moe_sort: routing needs float32 logits [rows, experts] and weights [rows, top]")
         n, top = chosen.shape
         tiles = tile_expert.numel()
         if any(t.dtype != torch.int32 or not t.is_contiguous() for t in (chosen, tile_expert, pos_row, pos_slot, slot_pos)) or \
@@ -993,7 +1000,7 @@ class Ops:
             raise KernelError("moe_sort: int32 lists, a tile's rows per tile, a place per slot")
         h = lib("moe")
         _check(h.kvad_moe_sort(_ptr(chosen), n * top, top, int(n_experts), tiles, int(tile_rows), _ptr(tile_expert), _ptr(pos_row), _ptr(pos_slot),
-                               _ptr(slot_pos), _stream()), h)
+                               _ptr(slot_pos), _ptr(logits), ld_z, _ptr(weight), _stream()), h)
 
     def gather_rows(self, a, pos_row, out) -> None:
         """out[p] = a[pos_row[p]], zeros where pos_row[p] < 0."""

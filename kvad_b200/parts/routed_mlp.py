@@ -90,12 +90,11 @@ class RoutedMLP(FeedForward):
         logits = ctx.buffer((n, (E + 3) // 4 * 4), torch.float32)[:, :E]
         self.router.forward(ctx, h, logits, "store_f32")
         chosen, weight = ctx.buffer((n, top), torch.int32), ctx.buffer((n, top), torch.float32)
-        ops.moe_route(logits, top, chosen, weight)
         tm = ops.moe_tile_rows(n, top, self.width % 8 == 0 and ff % 8 == 0)
         tiles = ops.moe_max_tiles(n, top, E, tm)
         tile_expert, slot_pos = ctx.buffer((tiles,), torch.int32), ctx.buffer((n * top,), torch.int32)
         pos_row, pos_slot = ctx.buffer((tiles * tm,), torch.int32), ctx.buffer((tiles * tm,), torch.int32)
-        ops.moe_sort(chosen, E, tm, tile_expert, pos_row, pos_slot, slot_pos)
+        ops.moe_sort(chosen, E, tm, tile_expert, pos_row, pos_slot, slot_pos, logits=logits, weight=weight)       # (routes, then groups)
         both = ctx.buffer((tiles * tm, 2 * ff))
         few = n * top <= ops.MOE_FEW_SLOTS      # (by the step's shape only)
         if tm == ops.MOE_WIDE_TILE:            # many rows: whole tiles on the tensor cores, from a copy of the rows in position order

@@ -5,7 +5,7 @@ pages that are freed and used again, the first tokens of a sequence, page border
 generation through the entry point.  The float32 engine is held to rounding of 32-bit sums against the oracle as
 it is.  In bfloat16 a router whose last chosen logit is nearly level with the next may choose the other way than
 the oracle, and what that row then writes stays in the state that later rows read; so the bfloat16 runs record
-which experts the engine chose (a wrapper around its routing kernel's call, graphs off), the oracle computes with
+which experts the engine chose (a wrapper around the call that routes and groups, graphs off), the oracle computes with
 those experts, and the choices themselves are compared with the oracle's own wherever its margin is not small."""
 import numpy as np
 import pytest
@@ -57,12 +57,12 @@ def engine(folders):
             assert e.use_graphs                           # every part's launches depend on the step's shape only
             e.routes = None
             if dtype == "bfloat16":
-                e.use_graphs, e.routes, inner = False, [], e.ops.moe_route
+                e.use_graphs, e.routes, inner = False, [], e.ops.moe_sort
 
-                def route(logits, top, chosen, weight):
-                    inner(logits, top, chosen, weight)
+                def sort(chosen, *args, **kwargs):                    # (the launch that routes the rows and groups them)
+                    inner(chosen, *args, **kwargs)
                     e.routes.append(chosen.clone())
-                e.ops.moe_route = route
+                e.ops.moe_sort = sort
         return cache[(name, dtype)]
     return get
 

@@ -175,6 +175,13 @@ def test_router_choice_with_ties_and_weights_over_the_chosen_only(E, top):
     ref_c, ref_w = pl.choose(z, top)
     assert np.array_equal(chosen.cpu().numpy(), ref_c)
     assert rel(weight, ref_w) < 1e-6
+    # the same inside the launch that groups the rows
+    chosen.fill_(-7), weight.fill_(float("nan"))
+    tiles = ops.moe_max_tiles(33, top, E, 32)
+    lists = [torch.empty(n, device="cuda", dtype=torch.int32) for n in (tiles, tiles * 32, tiles * 32, 33 * top)]
+    ops.moe_sort(chosen, E, 32, *lists, logits=padded, weight=weight)
+    assert np.array_equal(chosen.cpu().numpy(), ref_c) and rel(weight, ref_w) < 1e-6
+    assert sorted(lists[3].cpu().tolist()) == sorted(np.nonzero(lists[2].cpu().numpy() >= 0)[0].tolist())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
