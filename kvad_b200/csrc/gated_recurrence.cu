@@ -16,7 +16,7 @@
 // Everything after the projections is 32-bit: gates, their logarithms and exponentials, the unit vectors, the state,
 // the read-out and the per-head norm.  The columns of S (one per value entry) do not depend on one another, so a
 // block owns (sequence, head, 16 value columns) and walks the sequence's rows of this step in order; eight lanes
-// share a column, each with every eighth key entry of it in registers, and meet by three shuffles for the two dot
+// share a column, each with an eighth of its key entries in registers (four neighbours at a time), and meet by three shuffles for the two dot
 // products a row needs.  The rows' q, k and gates are staged 16 (or 8) rows at a time in shared memory, where the
 // scalar recurrences (the running maximum) and the transcendental functions are done once per block.  One row is
 // the same walk, so decoding, whole prompts and prompts in portions give the same bits.  The state of a slot is
@@ -44,6 +44,7 @@ struct RecArgs {
   float* state; int64_t state_stride;
   const int* seq_starts; const int* seq_slots;
   int heads, group, dk, dv, tiles;
+  int gates_ready;                     // delta rule: `gates` already holds the decays themselves (see decay_gate)
   float q_scale, cap;
 };
 
@@ -52,8 +53,8 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   constexpr int DKP = EPL * 8, TC = EPL >= 32 ? 8 : 16;
   constexpr int PER = TC * DKP / 128;          // staged q (k, gate) entries a thread carries from global to shared memory
   constexpr int VPER = TC * COLS / 128;
-  __shared__ float sq[TC][DKP], sk[TC][DKP];
-  __shared__ float sg[MODE == 1 ? TC : 1][MODE == 1 ? DKP : 1];
+  __shared__ __align__(16) float sq[TC][DKP], sk[TC][DKP];
+  __shared__ __align__(16) float sg[MODE == 1 ? TC : 1][MODE == 1 ? DKP : 4];
   __shared__ float sbias[MODE == 1 ? DKP : 1];
   __shared__ float sv[TC][COLS];
   __shared__ float s_a[TC], s_b[TC], s_c[TC], s_i[TC], s_f[TC];
@@ -75,10 +76,12 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   float* S_g = st + ((int64_t)h * dv + (col_ok ? col : 0)) * dk;
   float* n_g = st + (int64_t)p.heads * dv * dk + ((int64_t)h * p.tiles + blockIdx.x) * dk;
   float* m_g = st + (int64_t)p.heads * dv * dk + (int64_t)p.heads * p.tiles * dk + (int64_t)h * p.tiles + blockIdx.x;
+  // a lane's entries: four neighbouring key entries at a time, so that it reads q, k and the decays as 16-byte pieces
+  // and the eight lanes of a column read 128 bytes side by side: entry e of lane `sub` is key entry ((e / 4) * 8 + sub) * 4 + e % 4
   float S[EPL], N[MODE == 0 ? EPL : 1];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) {
-    const int d = e * 8 + sub;
+    const int d = (((e >> 2) * 8 + sub) << 2) + (e & 3);
     S[e] = (col_ok && d < dk) ? S_g[d] : 0.f;
     if (MODE == 0) N[e] = d < dk ? n_g[d] : 0.f;
   }
@@ -88,7 +91,10 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   const TI* v = reinterpret_cast<const TI*>(p.v);
 
   // the next rows' inputs are fetched into registers while the rows before them are walked
-  float rq[PER], rk[PER], rg[MODE == 1 ? PER : 1], rv[VPER], r0 = 0.f, r1 = 0.f;
+  // (as they are stored: a conversion here would wait for the load)
+  TI rq[PER], rk[PER], rv[VPER];
+  float rg[MODE == 1 ? PER : 1], r0 = 0.f, r1 = 0.f;
+  const TI zero = from_f32<TI>(0.f);
   auto fetch = [&](int c0) {
     const int nt = min(TC, row1 - c0);
 #pragma unroll
@@ -96,14 +102,14 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
       const int i = tid + j * 128, t = i / DKP, d = i - t * DKP;
       const int64_t r = c0 + t;
       const bool ok = t < nt && d < dk;
-      rq[j] = ok ? to_f32(q[r * p.ld_q + qh * dk + d]) : 0.f;
-      rk[j] = ok ? to_f32(k[r * p.ld_k + qh * dk + d]) : 0.f;
+      rq[j] = ok ? q[r * p.ld_q + qh * dk + d] : zero;
+      rk[j] = ok ? k[r * p.ld_k + qh * dk + d] : zero;
       if (MODE == 1) rg[j] = ok ? p.gates[r * p.ld_gates + h * dk + d] : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < VPER; ++j) {
       const int i = tid + j * 128, t = i / COLS, c = blockIdx.x * COLS + (i - t * COLS);
-      rv[j] = (t < nt && c < dv) ? to_f32(v[(int64_t)(c0 + t) * p.ld_v + h * dv + c]) : 0.f;
+      rv[j] = (t < nt && c < dv) ? v[(int64_t)(c0 + t) * p.ld_v + h * dv + c] : zero;
     }
     if (tid < nt) {
       if (MODE == 1) {
@@ -123,14 +129,14 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
       const int i = tid + j * 128, t = i / DKP, d = i - t * DKP;
-      sq[t][d] = rq[j] * p.q_scale;
-      sk[t][d] = rk[j];
-      if (MODE == 1) sg[t][d] = d < dk ? expf(-decay_rate * softplus_f(rg[j] + sbias[d])) : 1.f;
+      sq[t][d] = to_f32(rq[j]) * p.q_scale;
+      sk[t][d] = to_f32(rk[j]);
+      if (MODE == 1) sg[t][d] = d >= dk ? 1.f : (p.gates_ready ? rg[j] : expf(-decay_rate * softplus_f(rg[j] + sbias[d])));
     }
 #pragma unroll
     for (int j = 0; j < VPER; ++j) {
       const int i = tid + j * 128;
-      sv[i / COLS][i % COLS] = rv[j];
+      sv[i / COLS][i % COLS] = to_f32(rv[j]);
     }
     if (tid < nt) {
       if (MODE == 1) {
@@ -171,18 +177,25 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
       const float vj = sv[t][warp * 4 + grp];
-      float a = 0.f, b = 0.f, o;
+      const float4* k4 = reinterpret_cast<const float4*>(sk[t]) + sub;
+      const float4* q4 = reinterpret_cast<const float4*>(sq[t]) + sub;
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, o;       // (two partial sums each: half as long a chain)
       if (MODE == 0) {
         const float keep = s_a[t], take = s_b[t];
         const float tv = take * vj;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          const float kk = sk[t][e * 8 + sub], qq = sq[t][e * 8 + sub];
-          S[e] = fmaf(keep, S[e], tv * kk);
-          N[e] = fmaf(keep, N[e], take * kk);
-          a = fmaf(S[e], qq, a);
-          b = fmaf(N[e], qq, b);
+        for (int j = 0; j < EPL / 4; ++j) {
+          const float4 kk = k4[j * 8], qq = q4[j * 8];
+          float* Sj = S + 4 * j;
+          float* Nj = N + 4 * j;
+          Sj[0] = fmaf(keep, Sj[0], tv * kk.x); Sj[1] = fmaf(keep, Sj[1], tv * kk.y);
+          Sj[2] = fmaf(keep, Sj[2], tv * kk.z); Sj[3] = fmaf(keep, Sj[3], tv * kk.w);
+          Nj[0] = fmaf(keep, Nj[0], take * kk.x); Nj[1] = fmaf(keep, Nj[1], take * kk.y);
+          Nj[2] = fmaf(keep, Nj[2], take * kk.z); Nj[3] = fmaf(keep, Nj[3], take * kk.w);
+          a0 = fmaf(Sj[0], qq.x, a0); a1 = fmaf(Sj[1], qq.y, a1); a0 = fmaf(Sj[2], qq.z, a0); a1 = fmaf(Sj[3], qq.w, a1);
+          b0 = fmaf(Nj[0], qq.x, b0); b1 = fmaf(Nj[1], qq.y, b1); b0 = fmaf(Nj[2], qq.z, b0); b1 = fmaf(Nj[3], qq.w, b1);
         }
+        float a = a0 + a1, b = b0 + b1;
 #pragma unroll
         for (int o2 = 4; o2 > 0; o2 >>= 1) {
           a += __shfl_xor_sync(0xffffffffu, a, o2);
@@ -190,12 +203,18 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
         }
         o = a / (fmaxf(fabsf(b), s_c[t]) + 1e-6f);
       } else {
+        const float4* g4 = reinterpret_cast<const float4*>(sg[t]) + sub;
+        float4 kept_k[EPL / 4];
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          S[e] *= sg[t][e * 8 + sub];
-          a = fmaf(S[e], sk[t][e * 8 + sub], a);
-          b = fmaf(S[e], sq[t][e * 8 + sub], b);
+        for (int j = 0; j < EPL / 4; ++j) {
+          const float4 gg = g4[j * 8], kk = k4[j * 8], qq = q4[j * 8];
+          kept_k[j] = kk;
+          float* Sj = S + 4 * j;
+          Sj[0] *= gg.x; Sj[1] *= gg.y; Sj[2] *= gg.z; Sj[3] *= gg.w;
+          a0 = fmaf(Sj[0], kk.x, a0); a1 = fmaf(Sj[1], kk.y, a1); a0 = fmaf(Sj[2], kk.z, a0); a1 = fmaf(Sj[3], kk.w, a1);
+          b0 = fmaf(Sj[0], qq.x, b0); b1 = fmaf(Sj[1], qq.y, b1); b0 = fmaf(Sj[2], qq.z, b0); b1 = fmaf(Sj[3], qq.w, b1);
         }
+        float a = a0 + a1, b = b0 + b1;
 #pragma unroll
         for (int o2 = 4; o2 > 0; o2 >>= 1) {
           a += __shfl_xor_sync(0xffffffffu, a, o2);
@@ -203,7 +222,11 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
         }
         const float u = s_a[t] * (vj - a);
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) S[e] = fmaf(sk[t][e * 8 + sub], u, S[e]);
+        for (int j = 0; j < EPL / 4; ++j) {
+          float* Sj = S + 4 * j;
+          Sj[0] = fmaf(kept_k[j].x, u, Sj[0]); Sj[1] = fmaf(kept_k[j].y, u, Sj[1]);
+          Sj[2] = fmaf(kept_k[j].z, u, Sj[2]); Sj[3] = fmaf(kept_k[j].w, u, Sj[3]);
+        }
         o = fmaf(u, s_b[t], b);
       }
       if (sub == 0 && col_ok) p.out[(int64_t)(c0 + t) * p.ld_out + h * dv + col] = o;
@@ -212,7 +235,7 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
   if (row1 > row0) {
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
-      const int d = e * 8 + sub;
+      const int d = (((e >> 2) * 8 + sub) << 2) + (e & 3);
       if (col_ok && d < dk) S_g[d] = S[e];
       if (MODE == 0 && warp == 0 && grp == 0 && d < dk) n_g[d] = N[e];
     }
@@ -264,6 +287,22 @@ short_conv_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict__ t
       const float f = (hd < scaled_heads ? head_scale : 1.f) / sqrtf(sq + unit_eps);
       for (int d = lane; d < unit_dim; d += 32) hp[d] *= f;
     }
+  }
+}
+
+// g = exp(-exp(A_log_h) softplus(a + dt_bias)) in place on [rows, heads * dk]: for prompts, where every block of a head's
+// columns would otherwise work the same decays out again.
+__global__ void decay_gate_kernel(float* __restrict__ a, int64_t ld, const void* __restrict__ a_log, const void* __restrict__ dt_bias,
+                                  int params_f32, int n_rows, int heads, int dk) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int width = heads * dk;
+  const int64_t total = (int64_t)n_rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width;
+    const int c = (int)(i - r * width);
+    float* at = a + r * ld + c;
+    *at = expf(-expf(load_param(a_log, c / dk, params_f32)) * softplus_f(*at + load_param(dt_bias, c, params_f32)));
   }
 }
 
@@ -330,7 +369,7 @@ KVAD_EXPORT int kvad_gated_recurrence(int mode, int in_dtype, const void* q, int
                                       int64_t ld_v, const float* gates, int64_t ld_gates, const float* beta, int64_t ld_beta,
                                       const void* a_log, const void* dt_bias, int params_f32, float* out, int64_t ld_out, float* state,
                                       int64_t state_stride, const int* seq_starts, const int* seq_slots, int n_seqs, int heads,
-                                      int kv_heads, int dk, int dv, float q_scale, float cap, cudaStream_t stream) {
+                                      int kv_heads, int dk, int dv, float q_scale, float cap, int gates_ready, cudaStream_t stream) {
   KVAD_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0 && n_seqs >= 0,
                "gated_recurrence: bad sizes heads=%d kv_heads=%d dk=%d dv=%d", heads, kv_heads, dk, dv);
   KVAD_REQUIRE(dk <= 256, "gated_recurrence: heads of up to 256 key entries, not %d", dk);
@@ -346,7 +385,7 @@ KVAD_EXPORT int kvad_gated_recurrence(int mode, int in_dtype, const void* q, int
   a.out = out; a.ld_out = ld_out; a.state = state; a.state_stride = state_stride;
   a.seq_starts = seq_starts; a.seq_slots = seq_slots;
   a.heads = heads; a.group = heads / kv_heads; a.dk = dk; a.dv = dv; a.tiles = (dv + COLS - 1) / COLS;
-  a.q_scale = q_scale; a.cap = cap;
+  a.q_scale = q_scale; a.cap = cap; a.gates_ready = gates_ready;
   if (in_dtype == KVAD_DTYPE_F32) {
     if (mode == 0) launch_recurrence<float, 0>(a, n_seqs, stream); else launch_recurrence<float, 1>(a, n_seqs, stream);
   } else if (in_dtype == KVAD_DTYPE_BF16) {
@@ -362,6 +401,18 @@ KVAD_EXPORT int kvad_gated_recurrence(int mode, int in_dtype, const void* q, int
 KVAD_EXPORT int kvad_gated_recurrence_state(int mode, int heads, int dk, int dv) {
   const int tiles = (dv + COLS - 1) / COLS;
   return heads * dv * dk + (mode == 0 ? heads * tiles * (dk + 1) : 0);
+}
+
+KVAD_EXPORT int kvad_decay_gate(float* a, int64_t ld, const void* a_log, const void* dt_bias, int params_f32, int n_rows, int heads, int dk,
+                                cudaStream_t stream) {
+  KVAD_REQUIRE(n_rows >= 0 && heads > 0 && dk > 0 && a && a_log && dt_bias && ld >= (int64_t)heads * dk, "decay_gate: bad arguments");
+  if (n_rows == 0) return KVAD_OK;
+  const int64_t total = (int64_t)n_rows * heads * dk;
+  const int64_t blocks = (total + 255) / 256;
+  kvad_launch(decay_gate_kernel, dim3((unsigned)(blocks < 148 * 16 ? blocks : 148 * 16)), dim3(256), 0, stream, a, ld, a_log, dt_bias, params_f32,
+              n_rows, heads, dk);
+  KVAD_CHECK_LAUNCH("decay_gate");
+  return KVAD_OK;
 }
 
 KVAD_EXPORT int kvad_short_conv(int dtype, const void* x, int64_t ld_x, const void* taps, float* y, int64_t ld_y, const float* state,

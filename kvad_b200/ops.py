@@ -111,8 +111,9 @@ _SIGNATURES = {
     "gated_recurrence": {
         "kvad_gated_recurrence": [c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                   c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_float, c_float, c_void_p],
+                                  c_int, c_int, c_float, c_float, c_int, c_void_p],
         "kvad_gated_recurrence_state": [c_int, c_int, c_int, c_int],
+        "kvad_decay_gate": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "kvad_short_conv": [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
         "kvad_conv_state": [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -867,13 +868,14 @@ class Ops:
         return int(lib("gated_recurrence").kvad_gated_recurrence_state(self.RECURRENCES[kind], int(n_heads), int(dk), int(dv)))
 
     def gated_recurrence(self, kind: str, q, k, v, gates, out, state, seq_starts, seq_slots, n_seqs: int, n_heads: int, n_kv_heads: int,
-                         dk: int, dv: int, *, q_scale: float = 1.0, cap: float = 0.0, beta=None, a_log=None, dt_bias=None) -> None:
+                         dk: int, dv: int, *, q_scale: float = 1.0, cap: float = 0.0, beta=None, a_log=None, dt_bias=None,
+                         gates_ready: bool = False) -> None:
         """Per sequence and head over the step's rows in order; `state` is `[slots, floats]` (32-bit), carried on.
         `matrix_memory`: S = exp(f + m' - m) S + exp(i - m) k v^T with the running maximum m, n likewise with k alone,
         o = S^T q / (max(|n.q|, exp(-m)) + 1e-6); `gates` float32 [rows, 2 heads] = raw input | forget projections, capped
         here (`cap` tanh(x / cap)), the forget gate through logsigmoid.  `delta_rule`: S = g * S per key channel,
         u = beta (v - S^T k), S += k u^T, o = S^T q; `gates` float32 [rows, heads x dk] raw, g = exp(-exp(a_log) softplus(gates +
-        dt_bias)); `beta` float32 [rows, heads].  q and k have `n_kv_heads` heads that the heads share in groups; `out` is
+        dt_bias)), or with `gates_ready` g itself (`decay_gate`); `beta` float32 [rows, heads].  q and k have `n_kv_heads` heads that the heads share in groups; `out` is
         float32 [rows, heads x dv], the raw read-out."""
         _need_cuda(q, k, v, gates, out, state, seq_starts, seq_slots, beta, a_log, dt_bias)
         mode = self.RECURRENCES[kind]
@@ -898,7 +900,17 @@ class Ops:
         _check(h.kvad_gated_recurrence(mode, _code(q.dtype), _ptr(q), ld_q, _ptr(k), ld_k, _ptr(v), ld_v, _ptr(gates), ld_g, _ptr(beta), ld_b,
                                        _ptr(a_log), _ptr(dt_bias), p_f32, _ptr(out), ld_o, _ptr(state), state.stride(0), _ptr(seq_starts),
                                        _ptr(seq_slots), int(n_seqs), int(n_heads), int(n_kv_heads), int(dk), int(dv), float(q_scale),
-                                       float(cap), _stream()), h)
+                                       float(cap), int(bool(gates_ready)), _stream()), h)
+
+    def decay_gate(self, a, a_log, dt_bias, n_heads: int, dk: int) -> None:
+        """In place on float32 `a` [rows, heads x dk]: g = exp(-exp(a_log_h) softplus(a + dt_bias))."""
+        _need_cuda(a, a_log, dt_bias)
+        if (a.dtype != torch.float32 or a.shape[1] != n_heads * dk or a_log.numel() != n_heads or dt_bias.numel() != n_heads * dk
+                or a_log.dtype != dt_bias.dtype or a_log.dtype not in (torch.float32, torch.bfloat16)):
+            raise KernelError("decay_gate: float32 rows [rows, heads x dk], A_log per head and dt_bias per head and key channel of one dtype")
+        h = lib("gated_recurrence")
+        _check(h.kvad_decay_gate(_ptr(a), _rows_view(a, "decay rows"), _ptr(a_log), _ptr(dt_bias), 1 if a_log.dtype == torch.float32 else 0,
+                                 a.shape[0], int(n_heads), int(dk), _stream()), h)
 
     def short_conv(self, x, taps, y, state, conv_off: int, row_seq, row_pos, seq_starts, seq_slots, *, n_sigmoid: int = 0,
                    unit_heads: int = 0, unit_dim: int = 0, scaled_heads: int = 0, head_scale: float = 1.0, unit_eps: float = 0.0) -> None:

@@ -89,8 +89,14 @@ class GatedDeltaRule(Mixer):
         gate = ctx.buffer((n, self.v_width))
         self.gate_up.forward(ctx, buf[:, self.proj.columns(5)], gate)
         raw = ctx.buffer((n, self.v_width), torch.float32)
+        # prompts: the decays once per row in a pass of their own (every block of a head's columns would work them out again);
+        # single-token rows: inside the recurrence, one launch fewer
+        ready = not ctx.batch.is_decode
+        if ready:
+            ops.decay_gate(decay, self.a_log, self.dt_bias, H, dk)
         ops.gated_recurrence("delta_rule", y[:, :G * dk], y[:, G * dk:2 * G * dk], y[:, 2 * G * dk:C], decay, raw, state, ctx.seq_starts,
-                             ctx.seq_slots, ctx.n_seqs, H, G, dk, self.value_dim, beta=y[:, C:C + H], a_log=self.a_log, dt_bias=self.dt_bias)
+                             ctx.seq_slots, ctx.n_seqs, H, G, dk, self.value_dim, beta=y[:, C:C + H], a_log=self.a_log, dt_bias=self.dt_bias,
+                             gates_ready=ready)
         mixed = ctx.buffer((n, self.v_width))
         ops.head_norm_gate(raw, gate, self.norm_weight, mixed, H, self.norm_eps, weight_per_head=False)
         self.out.forward(ctx, mixed, residual, "residual")

@@ -110,6 +110,15 @@ def test_delta_rule_keeps_a_first_key_that_nothing_overwrites(H, G, dk, dv):
         assert rel(out, np.concatenate([want[s][done[s]:done[s] + portion[s]] for s in live])) < 2e-5, portion
         for s in live:
             done[s] += portion[s]
+    # the decays worked out in a pass of their own (as for prompts): the same read-outs
+    state2, ready = torch.zeros_like(state), dev(np.concatenate([a[0].reshape(T, -1), a[1, :4].reshape(4, -1)]), torch.float32)
+    ops.decay_gate(ready, dev(a_log, torch.float32), dev(dt_bias.reshape(-1), torch.float32), H, dk)
+    assert rel(ready, np.concatenate([g[0].reshape(T, -1), g[1][:4].reshape(4, -1)])) < 1e-6
+    both = lambda x: dev(np.concatenate([x[0].reshape(T, -1), x[1, :4].reshape(4, -1)]), torch.float32)
+    out = torch.full((T + 4, H * dv), float("nan"), device="cuda")
+    ops.gated_recurrence("delta_rule", both(q), both(k), both(v), ready, out, state2, i32([0, T, T + 4]), i32(slots), 2, H, G, dk, dv, beta=both(beta),
+                         a_log=dev(a_log, torch.float32), dt_bias=dev(dt_bias.reshape(-1), torch.float32), gates_ready=True)
+    assert rel(out, np.concatenate([want[0], want[1]])) < 2e-5 and rel(state2, state.cpu().numpy()) < 1e-5
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
