@@ -193,7 +193,7 @@ def plan(c: VepinexConfig) -> ModelPlan:
 
 
 def random_tensors(c: VepinexConfig, rng) -> dict:
-    """Matrices ~N(0, 1/in), the embedding ~N(0, 1), norm weights around 1, gate biases and decays spread so that every
+    """Matrices ~N(0, 1/in), the embedding ~N(0, 1), norm weights near 1, gate biases and decays spread so that every
     branch of the gates is met, router biases small so that the router's matrix decides."""
     def mat(out, inp, gain=1.0):
         return rng.normal((out, inp), gain / math.sqrt(inp))
