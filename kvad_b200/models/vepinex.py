@@ -87,7 +87,7 @@ def read_config(view: JsonView) -> VepinexConfig:
             if float(_need(m, "gate_cap", where)) <= 0:
                 raise ConfigError(f"config: {where}: `gate_cap` must be positive")
         elif layer["type"] == "channel_delta":
-            kv = _pos_int(m, "kv_heads", where)
+            kv = _pos_int(m, "kv_heads", where) if m.get("kv_heads") is not None else heads      # (absent: a query/key head per head)
             if heads % kv:
                 raise ConfigError(f"config: {where}: {heads} heads do not divide into {kv} query/key heads")
             _pos_int(m, "conv", where)
@@ -149,7 +149,7 @@ def _mixer_spec(c: VepinexConfig, layer: dict) -> PartSpec:
                                           "gate_cap": m["gate_cap"], "norm_eps": c.norm_eps})
     if kind == "channel_delta":
         return PartSpec("gated_delta_rule", {
-            "width": c.width, "n_heads": m["heads"], "n_kv_heads": m["kv_heads"], "key_dim": m["dim"], "value_dim": m["vdim"],
+            "width": c.width, "n_heads": m["heads"], "n_kv_heads": m.get("kv_heads") or m["heads"], "key_dim": m["dim"], "value_dim": m["vdim"],
             "conv_taps": m["conv"], "decay_rank": m.get("decay_rank", DEFAULT_RANK), "gate_rank": m.get("gate_rank", DEFAULT_RANK),
             "norm_eps": c.norm_eps, "unit_eps": UNIT_EPS})
     return PartSpec("latent_attention", {
@@ -213,7 +213,7 @@ def random_tensors(c: VepinexConfig, rng) -> dict:
             t[p + "mix.i"], t[p + "mix.i.b"] = mat(H, w, 2.0), rng.normal((H,), 1.0)
             t[p + "mix.f"], t[p + "mix.f.b"] = mat(H, w, 2.0), rng.normal((H,), 1.0, 3.0)
         elif layer["type"] == "channel_delta":
-            G, taps = m["kv_heads"], m["conv"]
+            G, taps = m.get("kv_heads") or H, m["conv"]
             ra, rg = m.get("decay_rank", DEFAULT_RANK), m.get("gate_rank", DEFAULT_RANK)
             t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(G * dk, w, 2.0), mat(G * dk, w, 2.0), mat(H * dv, w, 2.0)
             for name, ch in (("q", G * dk), ("k", G * dk), ("v", H * dv)):

@@ -57,5 +57,13 @@ CONFIGS = {
     "D": model(54, 131,
                [delta(3, 3, 6, 10, 4, 3, 5), latent(3, 6, 2, 10, 10, base=100.0), mlstm(2, 6, 18, cap=8.0), latent(1, 10, 2, 14, 10, base=100.0, kv_from=1)],
                [moe(7, 3, 18, 1.0, shared=(10, 1.0)), dense(30), moe(3, 2, 14, 2.0), None]),
+    # larger and deeper: two latent layers with latents of their own, each read by a later layer; many small experts
+    "E": model(256, 1000,
+               [latent(4, 48, 16, 40, 96, base=1e5), mlstm(4, 48, 96, cap=12.0), delta(4, 2, 96, 48, 3, 12, 20), latent(6, 32, 16, 32, 96, base=1e5, kv_from=0),
+                delta(8, 8, 32, 32, 4, 8, 8), latent(2, 64, 64, 128, 160, base=3e4), mlstm(2, 128, 64), latent(8, 16, 64, 16, 160, base=3e4, kv_from=5)],
+               [moe(32, 4, 64, 1.0, shared=(192, 1.0)), dense(512), moe(32, 4, 64, 1.0, shared=(192, 1.0)), None, moe(12, 3, 96, 6.0), dense(384),
+                moe(32, 4, 64, 1.0, shared=(192, 1.0)), moe(5, 2, 200, 2.0, shared=(64, 0.5))]),
 }
-SEEDS = {"A": 101, "B": 202, "C": 303, "D": 404}
+SEEDS = {"A": 101, "B": 202, "C": 303, "D": 404, "E": 505}
+#: the configurations every test of the engine runs on; "E" has tests of its own
+SMALL = ("A", "B", "C", "D")
