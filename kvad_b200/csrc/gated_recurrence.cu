@@ -50,9 +50,9 @@ struct RecArgs {
 
 template <typename TI, int EPL, int MODE>
 __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
-  constexpr int DKP = EPL * 8, TC = EPL >= 32 ? 8 : 16;
+  constexpr int DKP = EPL * 8, TC = EPL >= 64 ? 4 : (EPL >= 32 ? 8 : 16);
   constexpr int PER = TC * DKP / 128;          // staged q (k, gate) entries a thread carries from global to shared memory
-  constexpr int VPER = TC * COLS / 128;
+  constexpr int VPER = TC * COLS >= 128 ? TC * COLS / 128 : 1;
   __shared__ __align__(16) float sq[TC][DKP], sk[TC][DKP];
   __shared__ __align__(16) float sg[MODE == 1 ? TC : 1][MODE == 1 ? DKP : 4];
   __shared__ float sbias[MODE == 1 ? DKP : 1];
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
 #pragma unroll
     for (int j = 0; j < VPER; ++j) {
       const int i = tid + j * 128, t = i / COLS, c = blockIdx.x * COLS + (i - t * COLS);
-      rv[j] = (t < nt && c < dv) ? v[(int64_t)(c0 + t) * p.ld_v + h * dv + c] : zero;
+      rv[j] = (t < nt && c < dv) ? v[(int64_t)(c0 + t) * p.ld_v + h * dv + c] : zero;      // (t < nt <= TC also where a block has more threads than values)
     }
     if (tid < nt) {
       if (MODE == 1) {
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(128) recurrence_kernel(const RecArgs p) {
 #pragma unroll
     for (int j = 0; j < VPER; ++j) {
       const int i = tid + j * 128;
-      sv[i / COLS][i % COLS] = to_f32(rv[j]);
+      if (i < TC * COLS) sv[i / COLS][i % COLS] = to_f32(rv[j]);
     }
     if (tid < nt) {
       if (MODE == 1) {
@@ -358,7 +358,8 @@ int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t stream) {
   if (epl <= 4) kvad_launch(recurrence_kernel<TI, 4, MODE>, grid, block, 0, stream, a);
   else if (epl <= 8) kvad_launch(recurrence_kernel<TI, 8, MODE>, grid, block, 0, stream, a);
   else if (epl <= 16) kvad_launch(recurrence_kernel<TI, 16, MODE>, grid, block, 0, stream, a);
-  else kvad_launch(recurrence_kernel<TI, 32, MODE>, grid, block, 0, stream, a);
+  else if (epl <= 32) kvad_launch(recurrence_kernel<TI, 32, MODE>, grid, block, 0, stream, a);
+  else kvad_launch(recurrence_kernel<TI, 64, MODE>, grid, block, 0, stream, a);
   return 0;
 }
 
@@ -372,7 +373,7 @@ KVAD_EXPORT int kvad_gated_recurrence(int mode, int in_dtype, const void* q, int
                                       int kv_heads, int dk, int dv, float q_scale, float cap, int gates_ready, cudaStream_t stream) {
   KVAD_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0 && n_seqs >= 0,
                "gated_recurrence: bad sizes heads=%d kv_heads=%d dk=%d dv=%d", heads, kv_heads, dk, dv);
-  KVAD_REQUIRE(dk <= 256, "gated_recurrence: heads of up to 256 key entries, not %d", dk);
+  KVAD_REQUIRE(dk <= 512, "gated_recurrence: heads of up to 512 key entries, not %d", dk);
   KVAD_REQUIRE(mode == 0 || mode == 1, "gated_recurrence: mode %d", mode);
   KVAD_REQUIRE(q && k && v && gates && out && state && seq_starts && seq_slots, "gated_recurrence: a pointer is missing");
   KVAD_REQUIRE(mode == 0 || (beta && a_log && dt_bias), "gated_recurrence: the delta rule needs beta, A_log and dt_bias");

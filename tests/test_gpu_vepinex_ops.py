@@ -43,7 +43,7 @@ def packed(lengths):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,dk,dv", [(3, 20, 24), (1, 72, 16), (2, 8, 40), (2, 200, 5)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 20, 24), (1, 72, 16), (2, 8, 40), (2, 200, 5), (1, 320, 20)])
 def test_matrix_memory_in_portions_with_gates_beyond_the_cap(dtype, H, dk, dv):
     rng, ops, cap = np.random.default_rng(dk), Ops(DT[dtype]), 6.0
     total_lens, slots = [150, 9, 1], [4, 0, 2]
@@ -75,7 +75,7 @@ def test_matrix_memory_in_portions_with_gates_beyond_the_cap(dtype, H, dk, dv):
     assert float(state[[1, 3, 5]].abs().max()) == 0.0          # slots of no sequence are untouched
 
 
-@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 16, 10), (2, 1, 136, 16), (3, 3, 6, 33), (6, 1, 40, 8)])
+@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 16, 10), (2, 1, 136, 16), (3, 3, 6, 33), (6, 1, 40, 8), (2, 2, 500, 18)])
 def test_delta_rule_keeps_a_first_key_that_nothing_overwrites(H, G, dk, dv):
     rng, ops = np.random.default_rng(dk + dv), Ops(torch.float32)
     lens, slots = [300, 4], [1, 5]
