@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(256)
 grouped_rows_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict__ in_rows, const T* __restrict__ w,
                     int64_t expert_stride, TO* __restrict__ out, int64_t ld_out, const int* __restrict__ out_rows,
                     const int* __restrict__ valid, const int* __restrict__ tile_expert, int n_out, int k_dim) {
-  constexpr int R = 8, CU = 2, PIECE = 16 / (int)sizeof(T);
+  constexpr int R = 8, CU = 2, PIECE = 16 / (int)sizeof(T);       // (four outputs a warp: 4 % slower on the step, fewer blocks and more registers)
   __shared__ int rows_in[TM], rows_out[TM], n_valid;
   pdl_launch_dependents();
   pdl_wait();
@@ -256,24 +256,25 @@ grouped_rows_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict
   const int col0 = (blockIdx.x * 8 + warp) * CU;
   if (col0 >= n_out) return;
   const T* we = w + (int64_t)expert * expert_stride;
-  const T* w0 = we + (int64_t)col0 * k_dim;
-  const T* w1 = we + (int64_t)(col0 + 1 < n_out ? col0 + 1 : col0) * k_dim;
+  const T* wr[CU];
+#pragma unroll
+  for (int c = 0; c < CU; ++c) wr[c] = we + (int64_t)(col0 + c < n_out ? col0 + c : col0) * k_dim;
   for (int r0 = 0; r0 < n_valid; r0 += R) {
     const int nr = min(R, n_valid - r0);
     float acc[R][CU] = {};
 #pragma unroll 4
     for (int k = lane * PIECE; k < k_dim; k += 32 * PIECE) {
-      float wa[PIECE], wb[PIECE], av[PIECE];
-      load_piece<T, PIECE>(w0 + k, PIECE, true, wa);
-      load_piece<T, PIECE>(w1 + k, PIECE, true, wb);
+      float wv[CU][PIECE], av[PIECE];
+#pragma unroll
+      for (int c = 0; c < CU; ++c) load_piece<T, PIECE>(wr[c] + k, PIECE, true, wv[c]);
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         if (r < nr) {
           load_piece<T, PIECE>(a + (int64_t)rows_in[r0 + r] * ld_a + k, PIECE, true, av);
 #pragma unroll
           for (int j = 0; j < PIECE; ++j) {
-            acc[r][0] = fmaf(av[j], wa[j], acc[r][0]);
-            acc[r][1] = fmaf(av[j], wb[j], acc[r][1]);
+#pragma unroll
+            for (int c = 0; c < CU; ++c) acc[r][c] = fmaf(av[j], wv[c][j], acc[r][c]);
           }
         }
       }
@@ -281,14 +282,44 @@ grouped_rows_kernel(const T* __restrict__ a, int64_t ld_a, const int* __restrict
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (r < nr) {
-        const float s0 = warp_sum(acc[r][0]), s1 = warp_sum(acc[r][1]);
+        float sums[CU];
+#pragma unroll
+        for (int c = 0; c < CU; ++c) sums[c] = warp_sum(acc[r][c]);
         if (lane == 0) {
           TO* o = out + (int64_t)rows_out[r0 + r] * ld_out + col0;
-          o[0] = from_f32<TO>(s0);
-          if (col0 + 1 < n_out) o[1] = from_f32<TO>(s1);
+#pragma unroll
+          for (int c = 0; c < CU; ++c)
+            if (col0 + c < n_out) o[c] = from_f32<TO>(sums[c]);
         }
       }
     }
+  }
+}
+
+__device__ __forceinline__ float clamped_glu_f(float gate, float up, float limit, float alpha) {
+  const float g = fminf(gate, limit);
+  const float u = fminf(fmaxf(up, -limit), limit);
+  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
+// Eight neighbouring columns a thread, as 16-byte pieces (bfloat16 with sizes and addresses in whole pieces).
+__global__ void clamped_glu_vec_kernel(const __nv_bfloat16* __restrict__ gate, int64_t ld_g, const __nv_bfloat16* __restrict__ up, int64_t ld_u,
+                                       __nv_bfloat16* __restrict__ out, int64_t ld_o, int n_rows, int width, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = width / 8;
+  const int64_t total = (int64_t)n_rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int c = (int)(i - r * per_row) * 8;
+    float g[8], u[8];
+    load_piece<__nv_bfloat16, 8>(gate + r * ld_g + c, 8, true, g);
+    load_piece<__nv_bfloat16, 8>(up + r * ld_u + c, 8, true, u);
+    __nv_bfloat162 y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      y[j] = __floats2bfloat162_rn(clamped_glu_f(g[2 * j], u[2 * j], limit, alpha), clamped_glu_f(g[2 * j + 1], u[2 * j + 1], limit, alpha));
+    *reinterpret_cast<uint4*>(out + r * ld_o + c) = *reinterpret_cast<const uint4*>(y);
   }
 }
 
@@ -300,9 +331,30 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate, int64_t ld_g, con
   const int64_t total = (int64_t)n_rows * width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / width, c = i - r * width;
-    const float g = fminf(to_f32(gate[r * ld_g + c]), limit);
-    const float u = fminf(fmaxf(to_f32(up[r * ld_u + c]), -limit), limit);
-    out[r * ld_o + c] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    out[r * ld_o + c] = from_f32<T>(clamped_glu_f(to_f32(gate[r * ld_g + c]), to_f32(up[r * ld_u + c]), limit, alpha));
+  }
+}
+
+// Four neighbouring columns a thread (widths and strides in fours, 16-byte aligned bases); the choices in the same order.
+__global__ void moe_combine_vec_kernel(float* __restrict__ residual, const float* __restrict__ outs, int64_t ld_outs,
+                                       const int* __restrict__ slot_pos, const float* __restrict__ weight, int n_rows, int width, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = width / 4;
+  const int64_t total = (int64_t)n_rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int c = (int)(i - r * per_row) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top; ++k) {
+      const float wk = weight[r * top + k];
+      const float4 v = *reinterpret_cast<const float4*>(outs + (int64_t)slot_pos[r * top + k] * ld_outs + c);
+      acc.x = fmaf(wk, v.x, acc.x); acc.y = fmaf(wk, v.y, acc.y); acc.z = fmaf(wk, v.z, acc.z); acc.w = fmaf(wk, v.w, acc.w);
+    }
+    float4* at = reinterpret_cast<float4*>(residual + r * width + c);
+    float4 x = *at;
+    x.x += acc.x; x.y += acc.y; x.z += acc.z; x.w += acc.w;
+    *at = x;
   }
 }
 
@@ -398,6 +450,10 @@ KVAD_EXPORT int kvad_clamped_glu(int dtype, const void* gate, int64_t ld_g, cons
   if (dtype == KVAD_DTYPE_F32)
     kvad_launch(clamped_glu_kernel<float>, grid, block, 0, stream, (const float*)gate, ld_g, (const float*)up, ld_u, (float*)out, ld_o, n_rows,
                 width, limit, alpha);
+  else if (dtype == KVAD_DTYPE_BF16 && width % 8 == 0 && ld_g % 8 == 0 && ld_u % 8 == 0 && ld_o % 8 == 0 &&
+           ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+    kvad_launch(clamped_glu_vec_kernel, dim3(flat_blocks((int64_t)n_rows * (width / 8), 256)), block, 0, stream, (const __nv_bfloat16*)gate, ld_g,
+                (const __nv_bfloat16*)up, ld_u, (__nv_bfloat16*)out, ld_o, n_rows, width, limit, alpha);
   else if (dtype == KVAD_DTYPE_BF16)
     kvad_launch(clamped_glu_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)gate, ld_g, (const __nv_bfloat16*)up, ld_u,
                 (__nv_bfloat16*)out, ld_o, n_rows, width, limit, alpha);
@@ -429,8 +485,12 @@ KVAD_EXPORT int kvad_moe_combine(float* residual, const float* outs, int64_t ld_
                                  int width, int top, cudaStream_t stream) {
   KVAD_REQUIRE(n_rows >= 0 && width > 0 && top > 0 && residual && outs && slot_pos && weight, "moe_combine: bad arguments");
   if (n_rows == 0) return KVAD_OK;
-  kvad_launch(moe_combine_kernel, dim3(flat_blocks((int64_t)n_rows * width, 256)), dim3(256), 0, stream, residual, outs, ld_outs, slot_pos,
-              weight, n_rows, width, top);
+  if (width % 4 == 0 && ld_outs % 4 == 0 && ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(outs)) & 15) == 0)
+    kvad_launch(moe_combine_vec_kernel, dim3(flat_blocks((int64_t)n_rows * (width / 4), 256)), dim3(256), 0, stream, residual, outs, ld_outs,
+                slot_pos, weight, n_rows, width, top);
+  else
+    kvad_launch(moe_combine_kernel, dim3(flat_blocks((int64_t)n_rows * width, 256)), dim3(256), 0, stream, residual, outs, ld_outs, slot_pos,
+                weight, n_rows, width, top);
   KVAD_CHECK_LAUNCH("moe_combine");
   return KVAD_OK;
 }
